@@ -377,33 +377,43 @@ float b200_engine_last_decode_ms(const b200_engine* e);
 /* ------------------------------------------------------------------------- */
 /* x[t] = embed[tokens[t]] * scale */
 int b200_lm_embed(const int* tokens, const void* embed, float scale, float* x, int T, int W, int vocab, void* stream);
-/* cs[t][i] = (cos, sin)(pos[t] * inv_freq[i]), angle in double precision; inv_freq[half] doubles on the device */
-int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T, int half, void* stream);
+/* cs[t][i] = amp * (cos, sin)(pos[t] * inv_freq[i]), angle in double precision; inv_freq[half] doubles on the device */
+int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T, int half, float amp, void* stream);
 /* n = y / sqrt(mean(y^2) + eps) * (w_offset + w); x = n or (add) x += n.  wgt != NULL: y row t is the weighted
- * sum of rows t*top .. t*top+top-1 of y.  rows != NULL: the input row of output t is rows[t]. */
+ * sum of rows t*top .. t*top+top-1 of y.  rows != NULL: the input row of output t is rows[t].  center: y's mean is
+ * taken off first (a layer norm without bias). */
 int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const void* w, float w_offset, float eps,
-                      float* x, long ldx, int add, const int* rows, int T, int N, void* stream);
+                      float* x, long ldx, int add, const int* rows, int center, int T, int N, void* stream);
 /* D[t] = [q latent | kv latent | rotated key part] (the fused down-projection): cq = rmsnorm(q latent) * wq;
  * own_kv: rmsnorm(kv latent) * wkv and the rotated part go to cache[slot[t]][pos[t]] = [kv_rank | rot_dim] */
 int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wkv, float eps, float* cq, long ldq,
                         void* cache, int cache_bf16, long slot_stride, long tok_stride, const int* slot,
                         const int* pos, const float* cs, int q_rank, int kv_rank, int rot_dim, int rot_dims,
-                        int own_kv, int T, void* stream);
-/* qa[t][h][kv_rank + i] = rotate-half rotary of q[t][h][dim + i] (first rot_dims of rot_dim) */
+                        int own_kv, int pairs, int T, void* stream);
+/* qa[t][h][kv_rank + i] = rotary of q[t][h][dim + i] (first rot_dims of rot_dim; pairs (i, i + rot_dims/2), or
+ * (2i, 2i + 1) with `pairs`; q_rank 0 in latent_post: no query latent, D[t] = [kv latent | rotated key part]) */
 int b200_lm_rope_q(const float* q, long ldq, int qh_stride, int dim, float* qa, long ldqa, int Dl, int kv_rank,
-                   const float* cs, int H, int rot_dim, int rot_dims, int T, void* stream);
+                   const float* cs, int H, int rot_dim, int rot_dims, int pairs, int T, void* stream);
 /* absorbed latent attention: out[t][h] = softmax_j(scale * qa[t][h] . cache[slot[t]][j]) . cache[..][j][0:kv_rank],
- * j = 0..pos[t].  n_split > 1 (decode: few queries, many keys): the key tiles are dealt to n_split blocks per
+ * j = 0..pos[t] (window > 0: j = max(0, pos[t] - window + 1)..pos[t]).  n_split > 1 (decode: few queries, many keys): the key tiles are dealt to n_split blocks per
  * (token, head group), partial sums go to part [T][H][n_split][kv_rank + 2] and a second kernel merges them */
 int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int cache_bf16, long slot_stride,
                              long tok_stride, const int* slot, const int* pos, float* out, long ldo, int H, int Dl,
-                             int kv_rank, float scale, int round_q, float* part, int n_split, int T, void* stream);
+                             int kv_rank, float scale, int round_q, int window, float* part, int n_split, int T,
+                             void* stream);
 /* the `top` largest of z[t][0..E) (lowest index wins a tie) and the softmax over them */
 int b200_lm_router_topk(const float* z, long ldz, int E, int top, int* idx, float* wgt, int T, void* stream);
+/* s = sigmoid(z); the `top` largest of s + correction among the experts of the `keep` best of n_groups equal groups
+ * of neighbours (a group's score: the sum of its two largest s + correction); weights = chosen s / (their sum + 1e-20) */
+int b200_lm_router_group_topk(const float* z, long ldz, const void* correction, int E, int top, int n_groups, int keep,
+                              int* idx, float* wgt, int T, void* stream);
+/* x[t] += ls * (sum_s wgt[t][s] y[t top + s] (top = 0: y[t]) + sigmoid(sgate[t]) shared[t] (if shared)); ls: bf16 [N] or NULL */
+int b200_lm_residual_rows(const float* y, long ldy, const float* wgt, int top, const float* shared, long lds,
+                          const float* sgate, long ldsg, const void* ls, float* x, long ldx, int T, int N, void* stream);
 /* list[e][0..count[e]) = the entries i (ascending) with idx[i] == e */
 int b200_lm_moe_group(const int* idx, int n_entries, int E, int* list, long list_stride, int* count, void* stream);
 /* Y[b][r][n] = epi(sum_k X[b][xr][k] W[b][n][k] + bias[n]); list/count: rows of batch b are the entries
- * list[b][0..count[b]), x row = entry / x_div, y row = entry.  epi 0 none, 1 relu^2, 2 p*tanh(v/p).
+ * list[b][0..count[b]), x row = entry / x_div, y row = entry.  epi 0 none, 1 relu^2, 2 p*tanh(v/p), 4 v*p.
  * skinny != 0: the decode kernels (weight rows streamed once for the few rows of X).  compact > 0 (skinny, with
  * counts): at most `compact` batches have rows, and only that many slices are launched (slice z = the z-th batch
  * whose count is not zero). */
@@ -440,11 +450,11 @@ int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* acti
 /* tokens one after the other: first[t] = row of the first token of t's        */
 /* sequence, seqs[g] = (first row, rows).  State buffers are fp32 per slot.    */
 /* ------------------------------------------------------------------------- */
-/* Y[t][c] = act(sum_j w[c][j] U[t - (taps-1) + j][c]); inputs before the step come from state[slot] = the
+/* Y[t][c] = act(bias[c] + sum_j w[c][j] U[t - (taps-1) + j][c]) (bias may be NULL); inputs before the step come from state[slot] = the
  * taps-1 inputs before the step's first token ([taps-1][C]), zeros before position 0; the state is then advanced */
 int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
                        const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
-                       int act, int T, void* stream);
+                       int act, const void* bias, int T, void* stream);
 /* rotate-half rotary (first rot_dims of every head) on Q in place and on K; cache[slot[t]][pos[t]] = [K | V] */
 int b200_lm_qkv_post(float* Q, long ldq, const float* K, long ldk, const float* V, long ldv, void* cache, int cache_bf16,
                      long slot_stride, long tok_stride, const int* slot, const int* pos, const float* cs, int H, int G,
@@ -459,25 +469,28 @@ int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cach
 /* per head a (dim, vdim) state carried through each sequence: S <- decay S + k u^T, out = S^T q, u = v or
  * (delta) beta (v - (decay S)^T k); decay per head (decay_const) or exp(-exp(A_log) softplus(a + dt_bias)) per
  * token; beta = sigmoid(b) or 1; q, k shared by `rep` heads, optionally silu'd (act) and scaled to unit length.
+ * dt_in (state-space form): u = softplus(a + dt_bias) v; skip != NULL ([H], bf16): out += skip[h] v.
  * prep != NULL (a prompt step; T tokens): scratch of T * (2 (H / rep) dim + H / rep + 2 H) floats — the per-token work
  * (activation, unit lengths, k . q, decay, beta) runs first as one parallel pass and the walk reads its results */
 int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv, float* out, long ldo,
                          float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
                          int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
                          const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
-                         const float* b, long ldb, int delta, float* prep, int T, void* stream);
+                         const float* b, long ldb, int delta, int dt_in, const void* skip, float* prep, int T,
+                         void* stream);
 /* operands of the tensor-core attention of a prompt step: out[(t, r)] = bf16 of q[t][r * dim .. + dim) padded to Kp;
  * P[(t, r)][j] = softmax over the visible keys key0 + j (and sink[r]) of scale * S[(t, r)][j], bf16, zero elsewhere */
 int b200_lm_heads_to_bf16(const float* q, long ldq, int rep, int dim, void* out, int Kp, int T, void* stream);
 int b200_lm_sink_softmax_bf16(const float* S, long lds, const int* pos, int rep, const void* sink, float scale, int chunk,
                               int window, int key0, void* P, long ldp, int rows, int Sp, void* stream);
-/* out[t][c] = scale * o[t][c] * [rsqrt(mean over c's group of `span` + eps)] * [w[c mod w_len]] * [act(gate)] */
+/* out[t][c] = scale * o[t][c] * [rsqrt(mean over c's group of `span` + eps)] * [w[c mod w_len]] * [act(gate)];
+ * gate_first: the gate is applied before the norm (the mean square is that of the gated numbers) */
 int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, const void* w, int w_len, float eps, int span,
-                      int gate_per_head, int gate_silu, int dv, int n, float scale, float* out, long ldo, int T,
-                      void* stream);
-/* Y = g sigmoid(alpha g) (u + 1), g = min(G, limit), u = clamp(U, -limit, limit) */
-int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float* Y, long ldy,
-                      int n, int T, void* stream);
+                      int gate_per_head, int gate_silu, int dv, int n, float scale, float* out, long ldo, int gate_first,
+                      int T, void* stream);
+/* Y = g sigmoid(alpha g) (u + up_off), g = min(G, limit), u = clamp(U, -limit, limit) */
+int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
+                      float* Y, long ldy, int n, int T, void* stream);
 
 #ifdef __cplusplus
 }

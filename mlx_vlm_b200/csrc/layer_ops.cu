@@ -48,20 +48,22 @@ __global__ void embed_scale_kernel(const int* __restrict__ tok, const bf16* __re
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// rotary table: cs[t][i] = (cos, sin)(pos[t] * inv_freq[i]) with the angle in double precision
+// rotary table: cs[t][i] = amp * (cos, sin)(pos[t] * inv_freq[i]) with the angle in double precision (amp: the
+// amplitude that a frequency scaling puts on both, 1 without one)
 __global__ void rope_table_kernel(const int* __restrict__ pos, const double* __restrict__ inv_freq,
-                                  float2* __restrict__ cs, int T, int half) {
+                                  float2* __restrict__ cs, int T, int half, float amp) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= T * half) return;
   const double a = (double)pos[i / half] * inv_freq[i % half];
   double s, c;
   sincos(a, &s, &c);
-  cs[i] = make_float2((float)c, (float)s);
+  cs[i] = make_float2((float)c * amp, (float)s * amp);
 }
 
 // ---------------------------------------------------------------------------------------------------------
 // RMS norm of y's rows (optionally the weighted sum of `top` rows of a scattered buffer), weight (w_offset + w),
-// then either out = norm or x += norm.  rows: optional gather list for the input row.
+// then either out = norm or x += norm.  rows: optional gather list for the input row.  center: the row's mean is
+// taken off first and the root mean square is that of the deviations (a layer norm without bias).
 struct NormP {
   const float* y; long ldy;
   const float* wgt; int top;          // combine: y row = sum_s wgt[t*top+s] * y[(t*top+s)]
@@ -70,6 +72,7 @@ struct NormP {
   int add;
   const int* rows;                    // input row of output t (NULL: t)
   int N;
+  int center;
 };
 __global__ void norm_rows_kernel(NormP p) {
   extern __shared__ float sm[];
@@ -87,12 +90,18 @@ __global__ void norm_rows_kernel(NormP p) {
       v = p.y[r * p.ldy + i];
     }
     row[i] = v;
-    ss += v * v;
+    ss += p.center ? v : v * v;
   }
-  const float tot = block_sum(ss, red);
+  float tot = block_sum(ss, red), mean = 0.f;
+  if (p.center) {                     // two passes over the staged row: mean, then the squared deviations
+    mean = tot / (float)p.N;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < p.N; i += blockDim.x) { const float d = row[i] - mean; ss = fmaf(d, d, ss); }
+    tot = block_sum(ss, red);
+  }
   const float inv = 1.0f / sqrtf(tot / (float)p.N + p.eps);
   for (int i = threadIdx.x; i < p.N; i += blockDim.x) {
-    const float v = row[i] * inv * (p.w_offset + bf2f(p.w[i]));
+    const float v = (row[i] - mean) * inv * (p.w_offset + bf2f(p.w[i]));
     float* o = p.x + (long)t * p.ldx + i;
     *o = p.add ? *o + v : v;
   }
@@ -111,16 +120,31 @@ struct LatentPostP {
   const int *slot, *pos;
   const float2* cs;                          // [T][rot_dims/2]
   int q_rank, kv_rank, rot_dim, rot_dims, own_kv;
+  int pairs;                                 // the rotation pairs (2i, 2i + 1) instead of (i, i + rot_dims / 2)
 };
+// element i of a vector r whose first `dims` numbers turn by the table row a[0 .. dims/2)
+__device__ __forceinline__ float rope_elem(const float* r, int i, int dims, const float2* a, int pairs) {
+  if (i >= dims) return r[i];
+  const int half = dims >> 1;
+  if (pairs) {
+    const float2 c = a[i >> 1];
+    return (i & 1) ? r[i] * c.x + r[i - 1] * c.y : r[i] * c.x - r[i + 1] * c.y;
+  }
+  if (i < half) { const float2 c = a[i]; return r[i] * c.x - r[i + half] * c.y; }
+  const float2 c = a[i - half];
+  return r[i] * c.x + r[i - half] * c.y;
+}
 template <typename CT>
 __global__ void latent_post_kernel(LatentPostP<CT> p) {
   __shared__ float red[32];
   const int t = blockIdx.x;
   const float* d = p.D + (long)t * p.ldd;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) ss += d[i] * d[i];
-  float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)p.q_rank + p.eps);
-  for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) p.cq[(long)t * p.ldq + i] = d[i] * inv * bf2f(p.wq[i]);
+  float ss = 0.f, inv = 0.f;
+  if (p.q_rank > 0) {                 // a design without a query latent has q_rank 0: the row starts with the kv latent
+    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) ss += d[i] * d[i];
+    inv = 1.0f / sqrtf(block_sum(ss, red) / (float)p.q_rank + p.eps);
+    for (int i = threadIdx.x; i < p.q_rank; i += blockDim.x) p.cq[(long)t * p.ldq + i] = d[i] * inv * bf2f(p.wq[i]);
+  }
   if (!p.own_kv) return;
   const float* k = d + p.q_rank;
   ss = 0.f;
@@ -130,40 +154,19 @@ __global__ void latent_post_kernel(LatentPostP<CT> p) {
   for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) st_act(c + i, k[i] * inv * bf2f(p.wkv[i]));
   const float* r = k + p.kv_rank;
   const int half = p.rot_dims / 2;
-  for (int i = threadIdx.x; i < p.rot_dim; i += blockDim.x) {
-    float v;
-    if (i < half) {
-      const float2 a = p.cs[(long)t * half + i];
-      v = r[i] * a.x - r[i + half] * a.y;
-    } else if (i < p.rot_dims) {
-      const float2 a = p.cs[(long)t * half + i - half];
-      v = r[i] * a.x + r[i - half] * a.y;
-    } else {
-      v = r[i];
-    }
-    st_act(c + p.kv_rank + i, v);
-  }
+  for (int i = threadIdx.x; i < p.rot_dim; i += blockDim.x)
+    st_act(c + p.kv_rank + i, rope_elem(r, i, p.rot_dims, p.cs + (long)t * half, p.pairs));
 }
 
 // rotated query parts into the absorbed query rows: qa[t][h][kv_rank + i] = rope(q[t][h][dim + i])
 __global__ void rope_q_kernel(const float* __restrict__ q, long ldq, int qh_stride, int dim, float* __restrict__ qa,
                               long ldqa, int Dl, int kv_rank, const float2* __restrict__ cs, int H, int rot_dim,
-                              int rot_dims) {
+                              int rot_dims, int pairs) {
   const int t = blockIdx.x, half = rot_dims / 2;
   for (int e = threadIdx.x; e < H * rot_dim; e += blockDim.x) {
     const int h = e / rot_dim, i = e % rot_dim;
     const float* r = q + (long)t * ldq + (long)h * qh_stride + dim;
-    float v;
-    if (i < half) {
-      const float2 a = cs[(long)t * half + i];
-      v = r[i] * a.x - r[i + half] * a.y;
-    } else if (i < rot_dims) {
-      const float2 a = cs[(long)t * half + i - half];
-      v = r[i] * a.x + r[i - half] * a.y;
-    } else {
-      v = r[i];
-    }
-    qa[(long)t * ldqa + (long)h * Dl + kv_rank + i] = v;
+    qa[(long)t * ldqa + (long)h * Dl + kv_rank + i] = rope_elem(r, i, rot_dims, cs + (long)t * half, pairs);
   }
 }
 
@@ -185,6 +188,7 @@ struct LatAttnP {
   int n_split;                           // key tiles are dealt round-robin to gridDim.z splits (decode: few queries,
                                          // many keys), a second kernel merges the splits
   int vec8;                              // bf16 cache rows start on 16-byte boundaries and Dl % 8 == 0
+  int window;                            // > 0: a query at position p sees the keys p - window + 1 .. p only
 };
 template <typename CT>
 __global__ void latent_attention_kernel(LatAttnP<CT> p) {
@@ -203,13 +207,14 @@ __global__ void latent_attention_kernel(LatAttnP<CT> p) {
     for (int i = lane; i < Dl; i += 32) qs[warp * Dl + i] = p.round_q ? rbf(q[i]) : q[i];
   }
   const int n_keys = p.pos[t] + 1;
+  const int key_lo = p.window > 0 ? max(n_keys - p.window, 0) : 0;
   const CT* base = p.cache + (long)p.slot[t] * p.slot_stride;
   const int per_lane = (p.kv_rank + 31) / 32;
   float m = -INFINITY, l = 0.f;
   float acc[32];                          // kv_rank <= 1024
 #pragma unroll
   for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-  for (int k0 = blockIdx.z * LA_KT; k0 < n_keys; k0 += LA_KT * p.n_split) {
+  for (int k0 = key_lo + blockIdx.z * LA_KT; k0 < n_keys; k0 += LA_KT * p.n_split) {
     const int nk = min(LA_KT, n_keys - k0);
     __syncthreads();
     if (sizeof(CT) == 2 && p.vec8) {         // bf16 rows as 16-byte loads
@@ -352,6 +357,101 @@ __global__ void router_topk_kernel(const float* __restrict__ z, long ldz, int E,
     for (int s = 0; s < top; ++s) wgt[(long)t * top + s] /= denom;
 }
 
+// router with sigmoid scores and a choice limited to groups of experts: s = sigmoid(z); the choice is made on
+// c = s + correction; the E experts form n_groups equal groups of neighbours, a group's score is the sum of its two
+// largest c (its only c when a group is one expert), and only experts of the `keep` best groups can be chosen (the
+// others count as minus infinity); the `top` largest c are chosen (lowest index wins a tie) and weighted by their s,
+// divided by the sum of the chosen s (+ 1e-20).  A warp per token; the choice scores of a token sit in shared memory.
+__global__ void router_group_topk_kernel(const float* __restrict__ z, long ldz, const bf16* __restrict__ corr, int E,
+                                         int top, int n_groups, int keep, int* __restrict__ idx,
+                                         float* __restrict__ wgt, int T) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int t = blockIdx.x * nw + warp;
+  if (t >= T) return;
+  float* c = sm + (long)warp * (E + n_groups);      // [E] choice scores, then [n_groups] group scores
+  float* gs = c + E;
+  const float* zr = z + (long)t * ldz;
+  for (int e = lane; e < E; e += 32) c[e] = 1.0f / (1.0f + expf(-zr[e])) + (corr ? bf2f(corr[e]) : 0.f);
+  __syncwarp();
+  if (n_groups > 1 && keep < n_groups) {
+    const int per = E / n_groups;
+    for (int g = lane; g < n_groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;             // the two largest of the group
+      for (int i = 0; i < per; ++i) {
+        const float v = c[g * per + i];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      gs[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    for (int s = 0; s < keep; ++s) {                  // the best group leaves the contest with a mark: NaN-free +inf
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (v > best || (v == best && g < bi) || bi == 0x7fffffff)) { best = v; bi = g; }
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+      }
+      __syncwarp();
+      if (lane == 0 && bi != 0x7fffffff) gs[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gs[e / per] != INFINITY) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  float denom = 0.f;
+  for (int s = 0; s < top; ++s) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = c[e];
+      if (v > best || (v == best && e < bi && v != -INFINITY)) { best = v; bi = e; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (bi >= E) bi = 0;                              // fewer choosable experts than `top`: the host refuses that
+    __syncwarp();
+    const float sc = 1.0f / (1.0f + expf(-zr[bi]));
+    denom += sc;
+    if (lane == 0) { c[bi] = -INFINITY; idx[(long)t * top + s] = bi; wgt[(long)t * top + s] = sc; }
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float inv = 1.0f / (denom + 1e-20f);
+    for (int s = 0; s < top; ++s) wgt[(long)t * top + s] *= inv;
+  }
+}
+
+// the residual update of a branch with a scale vector:  x[t] += ls * ( sum_s wgt[t][s] y[t top + s]  (top = 0: y[t])
+//                                                                    + sigmoid(sgate[t]) shared[t] )   (if shared)
+__global__ void residual_rows_kernel(const float* __restrict__ y, long ldy, const float* __restrict__ wgt, int top,
+                                     const float* __restrict__ shared, long lds, const float* __restrict__ sgate,
+                                     long ldsg, const bf16* __restrict__ ls, float* __restrict__ x, long ldx, int N) {
+  const long t = blockIdx.x;
+  const float sg = shared ? (sgate ? 1.0f / (1.0f + expf(-sgate[t * ldsg])) : 1.f) : 0.f;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < N; i += blockDim.x * gridDim.y) {
+    float v;
+    if (top > 0) {
+      v = 0.f;
+      for (int s = 0; s < top; ++s) v += wgt[t * top + s] * y[(t * top + s) * ldy + i];
+    } else {
+      v = y[t * ldy + i];
+    }
+    if (shared) v = fmaf(sg, shared[t * lds + i], v);
+    float* o = x + t * ldx + i;
+    *o = fmaf(ls ? bf2f(ls[i]) : 1.f, v, *o);
+  }
+}
+
 // group the (token, choice) entries by expert: list[e][0..count[e]) = entry numbers in ascending order
 __global__ void moe_group_kernel(const int* __restrict__ idx, int n_entries, int* __restrict__ list, long list_stride,
                                  int* __restrict__ count) {
@@ -391,7 +491,7 @@ struct GemmRowsP {
   const int* count;                      // per batch: rows (device); NULL: M rows, no list
   int x_div;
   int M, N, K;
-  int epi; float epi_param;              // 0 none, 1 relu^2, 2 param * tanh(v / param), 3 added to the output
+  int epi; float epi_param;              // 0 none, 1 relu^2, 2 param * tanh(v / param), 3 added to the output, 4 v * param
   int round_x;
   int compact, n_batch;                  // compact: blockIdx.z counts the batches that HAVE rows (count[b] > 0) —
 };                                       // a decode step launches top x rows slices, not one per expert
@@ -420,6 +520,7 @@ __device__ __forceinline__ int nth_active(const int* __restrict__ count, int n_b
 __device__ __forceinline__ float gemm_epi(float v, int epi, float param) {
   if (epi == 1) { v = fmaxf(v, 0.f); return v * v; }
   if (epi == 2) return param * tanhf(v / param);
+  if (epi == 4) return v * param;
   return v;
 }
 // epi 3: the product is added to what the output row holds (a residual stream that accumulates in place)
@@ -865,18 +966,18 @@ int b200_lm_embed(const int* tokens, const void* embed, float scale, float* x, i
   return B200_OK;
 }
 
-int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T, int half, void* st) {
+int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T, int half, float amp, void* st) {
   B200_REQUIRE(pos && inv_freq && cs && T > 0 && half > 0, "lm_rope_table: bad argument");
-  rope_table_kernel<<<cdiv((long)T * half, 256), 256, 0, (cudaStream_t)st>>>(pos, inv_freq, (float2*)cs, T, half);
+  rope_table_kernel<<<cdiv((long)T * half, 256), 256, 0, (cudaStream_t)st>>>(pos, inv_freq, (float2*)cs, T, half, amp);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
 
 int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const void* w, float w_offset, float eps,
-                      float* x, long ldx, int add, const int* rows, int T, int N, void* st) {
+                      float* x, long ldx, int add, const int* rows, int center, int T, int N, void* st) {
   B200_REQUIRE(y && w && x && T > 0 && N > 0, "lm_norm_rows: bad argument");
   B200_REQUIRE((N + 32) * 4 <= 48 * 1024, "lm_norm_rows: rows of %d numbers do not fit shared memory", N);
-  NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, x, ldx, add, rows, N};
+  NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, x, ldx, add, rows, N, center};
   norm_rows_kernel<<<T, T < 64 ? 1024 : 256, (N + 32) * sizeof(float), (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
   return B200_OK;
@@ -885,17 +986,17 @@ int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const
 int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wkv, float eps, float* cq, long ldq,
                         void* cache, int cache_bf16, long slot_stride, long tok_stride, const int* slot,
                         const int* pos, const float* cs, int q_rank, int kv_rank, int rot_dim, int rot_dims,
-                        int own_kv, int T, void* st) {
-  B200_REQUIRE(D && wq && cq && T > 0, "lm_latent_post: bad argument");
+                        int own_kv, int pairs, int T, void* st) {
+  B200_REQUIRE(D && T > 0 && q_rank >= 0 && (q_rank == 0 || (wq && cq)), "lm_latent_post: bad argument");
   B200_REQUIRE(!own_kv || (wkv && cache && slot && pos && cs), "lm_latent_post: a layer with its own latent needs a cache");
   B200_REQUIRE(rot_dims % 2 == 0 && rot_dims <= rot_dim, "lm_latent_post: rotated dims %d of %d", rot_dims, rot_dim);
   if (cache_bf16) {
     LatentPostP<bf16> p{D, ldd, (const bf16*)wq, (const bf16*)wkv, eps, cq, ldq, (bf16*)cache, slot_stride, tok_stride,
-                        slot, pos, (const float2*)cs, q_rank, kv_rank, rot_dim, rot_dims, own_kv};
+                        slot, pos, (const float2*)cs, q_rank, kv_rank, rot_dim, rot_dims, own_kv, pairs};
     latent_post_kernel<bf16><<<T, T < 64 ? 512 : 128, 0, (cudaStream_t)st>>>(p);
   } else {
     LatentPostP<float> p{D, ldd, (const bf16*)wq, (const bf16*)wkv, eps, cq, ldq, (float*)cache, slot_stride,
-                         tok_stride, slot, pos, (const float2*)cs, q_rank, kv_rank, rot_dim, rot_dims, own_kv};
+                         tok_stride, slot, pos, (const float2*)cs, q_rank, kv_rank, rot_dim, rot_dims, own_kv, pairs};
     latent_post_kernel<float><<<T, T < 64 ? 512 : 128, 0, (cudaStream_t)st>>>(p);
   }
   B200_CHECK_LAUNCH();
@@ -903,17 +1004,18 @@ int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wk
 }
 
 int b200_lm_rope_q(const float* q, long ldq, int qh_stride, int dim, float* qa, long ldqa, int Dl, int kv_rank,
-                   const float* cs, int H, int rot_dim, int rot_dims, int T, void* st) {
+                   const float* cs, int H, int rot_dim, int rot_dims, int pairs, int T, void* st) {
   B200_REQUIRE(q && qa && cs && T > 0, "lm_rope_q: bad argument");
   rope_q_kernel<<<T, 128, 0, (cudaStream_t)st>>>(q, ldq, qh_stride, dim, qa, ldqa, Dl, kv_rank, (const float2*)cs, H,
-                                                 rot_dim, rot_dims);
+                                                 rot_dim, rot_dims, pairs);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
 
 int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int cache_bf16, long slot_stride,
                              long tok_stride, const int* slot, const int* pos, float* out, long ldo, int H, int Dl,
-                             int kv_rank, float scale, int round_q, float* part, int n_split, int T, void* st) {
+                             int kv_rank, float scale, int round_q, int window, float* part, int n_split, int T,
+                             void* st) {
   B200_REQUIRE(qa && cache && slot && pos && out && T > 0 && H > 0, "lm_latent_attention: bad argument");
   if (n_split < 1 || !part) n_split = 1;
   B200_REQUIRE(n_split <= 64, "lm_latent_attention: at most 64 splits");
@@ -926,12 +1028,12 @@ int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int 
   if (cache_bf16) {
     if (first_use_on_device(&g_attn_attr_bf16))
       B200_CUDA(cudaFuncSetAttribute(latent_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    LatAttnP<bf16> p{qa, ldqa, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split, vec8};
+    LatAttnP<bf16> p{qa, ldqa, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split, vec8, window};
     latent_attention_kernel<bf16><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   } else {
     if (first_use_on_device(&g_attn_attr_f32))
       B200_CUDA(cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    LatAttnP<float> p{qa, ldqa, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split, 0};
+    LatAttnP<float> p{qa, ldqa, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, H, Dl, kv_rank, scale, round_q, part, n_split, 0, window};
     latent_attention_kernel<float><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   }
   B200_CHECK_LAUNCH();
@@ -946,6 +1048,29 @@ int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int 
 int b200_lm_router_topk(const float* z, long ldz, int E, int top, int* idx, float* wgt, int T, void* st) {
   B200_REQUIRE(z && idx && wgt && T > 0 && top > 0 && top <= E && E <= 2048, "lm_router_topk: bad argument");
   router_topk_kernel<<<cdiv(T, 4), 128, 0, (cudaStream_t)st>>>(z, ldz, E, top, idx, wgt, T);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_router_group_topk(const float* z, long ldz, const void* correction, int E, int top, int n_groups, int keep,
+                              int* idx, float* wgt, int T, void* st) {
+  B200_REQUIRE(z && idx && wgt && T > 0 && top > 0 && top <= E && E <= 2048, "lm_router_group_topk: bad argument");
+  B200_REQUIRE(n_groups >= 1 && E % n_groups == 0 && keep >= 1 && keep <= n_groups,
+               "lm_router_group_topk: %d experts in %d groups, %d kept", E, n_groups, keep);
+  B200_REQUIRE(top <= (long)keep * (E / n_groups), "lm_router_group_topk: %d experts chosen among %d", top, keep * (E / n_groups));
+  const int nw = 4;
+  router_group_topk_kernel<<<cdiv(T, nw), nw * 32, (size_t)nw * (E + n_groups) * sizeof(float), (cudaStream_t)st>>>(
+      z, ldz, (const bf16*)correction, E, top, n_groups, keep, idx, wgt, T);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_residual_rows(const float* y, long ldy, const float* wgt, int top, const float* shared, long lds,
+                          const float* sgate, long ldsg, const void* ls, float* x, long ldx, int T, int N, void* st) {
+  B200_REQUIRE(y && x && T > 0 && N > 0 && (top == 0 || wgt), "lm_residual_rows: bad argument");
+  const int by = T >= 64 ? 1 : (cdiv(N, 256) < 16 ? cdiv(N, 256) : 16);
+  residual_rows_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(y, ldy, wgt, wgt ? top : 0, shared, lds, sgate, ldsg,
+                                                                  (const bf16*)ls, x, ldx, N);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -26,7 +26,7 @@ __device__ __forceinline__ float silu_exact(float x) { return x / (1.0f + expf(-
 __device__ __forceinline__ float softplus_exact(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
 // ---------------------------------------------------------------------------------------------------------
-// short convolution: y[t][c] = act( sum_j w[c][j] * u[t - (taps - 1) + j][c] ), inputs before the step come from
+// short convolution: y[t][c] = act( bias[c] + sum_j w[c][j] * u[t - (taps - 1) + j][c] ), inputs before the step come from
 // the slot's state (the taps - 1 inputs that precede the step's first token), inputs before position 0 are zero
 struct ConvP {
   const float* U; long ldu;
@@ -35,13 +35,14 @@ struct ConvP {
   float* state; long slot_stride;  // per slot [taps - 1][C]
   const int *slot, *pos, *first;
   int C, taps, act;
+  const bf16* bias;                // [C] or NULL
 };
 __global__ void short_conv_kernel(ConvP p) {
   const int t = blockIdx.x;
   const int back = t - p.first[t], ps = p.pos[t];
   const float* st = p.state + (long)p.slot[t] * p.slot_stride;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.C; c += blockDim.x * gridDim.y) {
-    float a = 0.f;
+    float a = p.bias ? bf2f(p.bias[c]) : 0.f;
     for (int j = 0; j < p.taps; ++j) {
       const int lag = p.taps - 1 - j;
       float u = 0.f;
@@ -317,6 +318,8 @@ struct StateP {
   const bf16 *A_log, *dt_bias;
   const float* b; long ldb;         // beta = sigmoid(b[t][h]); NULL: 1
   int delta;
+  int dt_in;                        // state-space form: beta = softplus(a[t][h] + dt_bias[h]) (the step size) and u = beta v
+  const bf16* skip;                 // [H] or NULL: o += skip[h] v
 };
 // The per-token work of a prompt step in one parallel pass: q, k activated and scaled to unit length (a warp per
 // token and q/k head, the same order of sums as the walk's own staging), k . q, the decay and beta of every head.
@@ -331,6 +334,7 @@ struct StatePrepP {
   const float* a; long lda;
   const bf16 *A_log, *dt_bias;
   const float* b; long ldb;
+  int dt_in;
 };
 __global__ void state_prep_kernel(StatePrepP p) {
   const long t = blockIdx.x;
@@ -363,9 +367,9 @@ __global__ void state_prep_kernel(StatePrepP p) {
     if (lane == 0) p.kq[t * p.Hk + hk] = dot;
   }
   for (int h = threadIdx.x; h < p.H; h += blockDim.x) {
-    p.dec[t * p.H + h] = p.decay_const ? p.decay_const[h]
-        : expf(-expf(bf2f(p.A_log[h])) * softplus_exact(p.a[t * p.lda + h] + bf2f(p.dt_bias[h])));
-    p.bet[t * p.H + h] = p.b ? sigmoid_exact(p.b[t * p.ldb + h]) : 1.f;
+    const float dt = p.decay_const ? 0.f : softplus_exact(p.a[t * p.lda + h] + bf2f(p.dt_bias[h]));
+    p.dec[t * p.H + h] = p.decay_const ? p.decay_const[h] : expf(-expf(bf2f(p.A_log[h])) * dt);
+    p.bet[t * p.H + h] = p.dt_in ? dt : (p.b ? sigmoid_exact(p.b[t * p.ldb + h]) : 1.f);
   }
 }
 
@@ -424,6 +428,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
   };
   const float A = (p.decay_const || !raw) ? 0.f : expf(bf2f(p.A_log[h])), dtb = (p.decay_const || !raw) ? 0.f : bf2f(p.dt_bias[h]);
   const float dconst = p.decay_const ? p.decay_const[h] : 0.f;
+  const float skip = p.skip ? bf2f(p.skip[h]) : 0.f;
   request(0);
   for (int c0 = 0; c0 < rows; c0 += CT) {
     const int nc = min(CT, rows - c0);
@@ -443,8 +448,9 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     }
     if ((int)threadIdx.x < nc) {
       if (raw) {
-        dec[threadIdx.x] = p.decay_const ? dconst : expf(-A * softplus_exact(ra + dtb));
-        bet[threadIdx.x] = p.b ? sigmoid_exact(rb) : 1.f;
+        const float dt = p.decay_const ? 0.f : softplus_exact(ra + dtb);
+        dec[threadIdx.x] = p.decay_const ? dconst : expf(-A * dt);
+        bet[threadIdx.x] = p.dt_in ? dt : (p.b ? sigmoid_exact(rb) : 1.f);
       } else {
         dec[threadIdx.x] = ra; bet[threadIdx.x] = rb; kq[threadIdx.x] = rkq;
       }
@@ -494,9 +500,11 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
         dk += __shfl_xor_sync(0xffffffffu, dk, o);
         dq += __shfl_xor_sync(0xffffffffu, dq, o);
       }
-      float u = vs[tk][cj];
+      const float vin = vs[tk][cj];
+      float u = vin;
       if (p.delta) u = bet[tk] * (u - d * dk);
-      if (r == 0 && valid) *op = fmaf(u, kq[tk], d * dq);
+      else if (p.dt_in) u = bet[tk] * u;
+      if (r == 0 && valid) *op = fmaf(skip, vin, fmaf(u, kq[tk], d * dq));
 #pragma unroll
       for (int i = 0; i < LS_R; ++i) S[i] = fmaf(k_[i], u, d * S[i]);
     }
@@ -519,6 +527,7 @@ struct HeadPostP {
   int gate_per_head, gate_silu, dv, n;
   float scale;
   float* out; long ldo;
+  int gate_first;                  // the gate multiplies o BEFORE the norm (the mean square is that of the gated numbers)
 };
 __global__ void head_post_kernel(HeadPostP p) {
   // a norm group of up to 1024 numbers belongs to one warp (blockIdx.y counts warps' worth of groups), a longer one
@@ -537,7 +546,15 @@ __global__ void head_post_kernel(HeadPostP p) {
   if (p.span > 0) {
     float ss = 0.f;
 #pragma unroll 4
-    for (int i = me; i < span; i += step) { const float v = o[i]; ss = fmaf(v, v, ss); }
+    for (int i = me; i < span; i += step) {
+      float v = o[i];
+      if (p.gate_first && g) {
+        const int c = gi * span + i;
+        const float z = g[p.gate_per_head ? c / p.dv : c];
+        v *= p.gate_silu ? silu_exact(z) : sigmoid_exact(z);
+      }
+      ss = fmaf(v, v, ss);
+    }
     ss = warp_sum(ss);
     if (wide) {                                // fixed order: lanes, then the warps one after the other
       if (lane == 0) red[warp] = ss;
@@ -550,28 +567,32 @@ __global__ void head_post_kernel(HeadPostP p) {
 #pragma unroll 4
   for (int i = me; i < span; i += step) {
     const int c = gi * span + i;
-    float v = o[i] * inv;
-    if (p.w) v *= bf2f(p.w[c % p.w_len]);
+    float v = o[i], gv = 1.f;
     if (g) {
       const float z = g[p.gate_per_head ? c / p.dv : c];
-      v *= p.gate_silu ? silu_exact(z) : sigmoid_exact(z);
+      gv = p.gate_silu ? silu_exact(z) : sigmoid_exact(z);
     }
+    if (p.gate_first) v = v * gv * inv;
+    else v *= inv;
+    if (p.w) v *= bf2f(p.w[c % p.w_len]);
+    if (!p.gate_first) v *= gv;
     out[i] = v * p.scale;
   }
 }
 
-// gated feed-forward activation with clamps: g = min(a, lim), u = clamp(b, -lim, lim), y = g sigmoid(alpha g) (u + 1)
+// gated feed-forward activation with clamps: g = min(a, lim), u = clamp(b, -lim, lim), y = g sigmoid(alpha g) (u + up_off)
+// (lim = +inf, alpha = 1, up_off = 0: the plain silu-gated unit)
 __global__ void glu_clamp_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
-                                 float alpha, float* __restrict__ Y, long ldy, int n) {
+                                 float alpha, float up_off, float* __restrict__ Y, long ldy, int n) {
   const int t = blockIdx.x, i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float g = fminf(G[(long)t * ldg + i], lim);
   const float u = fminf(fmaxf(U[(long)t * ldu + i], -lim), lim);
-  Y[(long)t * ldy + i] = g * sigmoid_exact(alpha * g) * (u + 1.0f);
+  Y[(long)t * ldy + i] = g * sigmoid_exact(alpha * g) * (u + up_off);
 }
 // the same, four columns per thread (rows of whole, aligned 16-byte vectors)
 __global__ void glu_clamp4_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
-                                  float alpha, float* __restrict__ Y, long ldy, int n) {
+                                  float alpha, float up_off, float* __restrict__ Y, long ldy, int n) {
   const int t = blockIdx.x, i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
   const float4 a = *reinterpret_cast<const float4*>(G + (long)t * ldg + i);
@@ -581,7 +602,7 @@ __global__ void glu_clamp4_kernel(const float* __restrict__ G, long ldg, const f
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const float g = fminf(gs[e], lim), u = fminf(fmaxf(us[e], -lim), lim);
-    y[e] = g * sigmoid_exact(alpha * g) * (u + 1.0f);
+    y[e] = g * sigmoid_exact(alpha * g) * (u + up_off);
   }
   *reinterpret_cast<float4*>(Y + (long)t * ldy + i) = make_float4(y[0], y[1], y[2], y[3]);
 }
@@ -646,10 +667,10 @@ extern "C" {
 
 int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
                        const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
-                       int act, int T, void* st) {
+                       int act, const void* bias, int T, void* st) {
   B200_REQUIRE(U && w && Y && (state || taps == 1) && slot && pos && first && seqs && T > 0 && n_seq > 0 && C > 0 && taps > 0,
                "lm_short_conv: bad argument");     // one tap keeps nothing between steps
-  ConvP p{U, ldu, (const bf16*)w, Y, ldy, state, slot_stride, slot, pos, first, C, taps, act};
+  ConvP p{U, ldu, (const bf16*)w, Y, ldy, state, slot_stride, slot, pos, first, C, taps, act, (const bf16*)bias};
   const int by = cdiv(C, 256) < 8 ? cdiv(C, 256) : 8;
   short_conv_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
@@ -714,13 +735,14 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
                          float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
                          int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
                          const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
-                         const float* b, long ldb, int delta, float* prep, int T, void* st) {
+                         const float* b, long ldb, int delta, int dt_in, const void* skip, float* prep, int T, void* st) {
   B200_REQUIRE(q && k && v && out && state && seqs && slot && pos && n_seq > 0 && H > 0 && rep > 0 && H % rep == 0,
                "lm_linear_state: bad argument");
   B200_REQUIRE(dim > 0 && dim <= 32 * LS_R && vdim > 0, "lm_linear_state: key size %d not supported (at most %d)", dim, 32 * LS_R);
   B200_REQUIRE(decay_const || (a && A_log && dt_bias), "lm_linear_state: a decay per head, or the inputs of a computed one");
+  B200_REQUIRE(!dt_in || (!decay_const && !delta && !b), "lm_linear_state: the step size scales the input only in the plain form with a computed decay");
   StateP p{q, ldq, k, ldk, v, ldv, out, ldo, state, slot_stride, seqs, slot, pos, H, rep, dim, vdim, act, unit_eps, q_scale,
-           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta};
+           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta, dt_in, (const bf16*)skip};
   const cudaStream_t cs = (cudaStream_t)st;
   if (prep) {     // scratch of T * (2 Hk dim + Hk + 2 H) floats: the per-token work runs first, over all tokens at once
     B200_REQUIRE(T > 0, "lm_linear_state: the prepared path needs the number of tokens");
@@ -728,7 +750,7 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
     const long n = (long)Hk * dim;
     float *qn = prep, *kn = qn + (long)T * n, *kq = kn + (long)T * n, *dec = kq + (long)T * Hk, *bet = dec + (long)T * H;
     StatePrepP pp{q, ldq, k, ldk, qn, kn, n, kq, dec, bet, H, Hk, dim, act, unit_eps, q_scale, decay_const, a, lda,
-                  (const bf16*)A_log, (const bf16*)dt_bias, b, ldb};
+                  (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, dt_in};
     state_prep_kernel<<<T, 128, 0, cs>>>(pp);
     B200_CHECK_LAUNCH();
     p.q = qn; p.ldq = n; p.k = kn; p.ldk = n; p.kq_in = kq; p.dec_in = dec; p.bet_in = bet;
@@ -763,24 +785,25 @@ int b200_lm_sink_softmax_bf16(const float* S, long lds, const int* pos, int rep,
 }
 
 int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, const void* w, int w_len, float eps, int span,
-                      int gate_per_head, int gate_silu, int dv, int n, float scale, float* out, long ldo, int T, void* st) {
+                      int gate_per_head, int gate_silu, int dv, int n, float scale, float* out, long ldo, int gate_first,
+                      int T, void* st) {
   B200_REQUIRE(o && out && T > 0 && n > 0 && dv > 0 && n % dv == 0, "lm_head_post: bad argument");
   B200_REQUIRE(span == 0 || n % span == 0, "lm_head_post: norm groups of %d numbers in rows of %d", span, n);
   B200_REQUIRE(!w || w_len > 0, "lm_head_post: a weight needs its length");
-  HeadPostP p{o, ldi, gate, ldg, (const bf16*)w, w_len, eps, span, gate_per_head, gate_silu, dv, n, scale, out, ldo};
+  HeadPostP p{o, ldi, gate, ldg, (const bf16*)w, w_len, eps, span, gate_per_head, gate_silu, dv, n, scale, out, ldo, gate_first};
   const int grp = span > 0 ? span : dv, groups = n / grp;
   head_post_kernel<<<dim3(T, grp > 1024 ? groups : cdiv(groups, 8)), 256, 0, (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
 
-int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float* Y, long ldy,
-                      int n, int T, void* st) {
+int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
+                      float* Y, long ldy, int n, int T, void* st) {
   B200_REQUIRE(G && U && Y && T > 0 && n > 0, "lm_glu_clamp: bad argument");
   const bool v4 = n % 4 == 0 && ldg % 4 == 0 && ldu % 4 == 0 && ldy % 4 == 0 &&
                   (((uintptr_t)G | (uintptr_t)U | (uintptr_t)Y) & 15) == 0;
-  if (v4 && T > 16) glu_clamp4_kernel<<<dim3(T, cdiv(n, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, Y, ldy, n);
-  else glu_clamp_kernel<<<dim3(T, cdiv(n, 256)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, Y, ldy, n);
+  if (v4 && T > 16) glu_clamp4_kernel<<<dim3(T, cdiv(n, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, Y, ldy, n);
+  else glu_clamp_kernel<<<dim3(T, cdiv(n, 256)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, Y, ldy, n);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -18,7 +18,7 @@ import torch
 
 from . import _native as N
 from .models.decoder_blocks import StepCtx
-from .models.layer_ops import EPI_NONE, EPI_SOFTCAP, LayerOps
+from .models.layer_ops import EPI_NONE, EPI_SCALE, EPI_SOFTCAP, LayerOps
 
 
 class LayerEngine:
@@ -110,8 +110,11 @@ class LayerEngine:
                 layer.forward(ctx, x)
         n = x.shape[0] if want is None else want.shape[0]
         xn = ops.empty((n, c.width))
-        ops.norm_rows(x, c.final_norm, c.eps, xn, w_offset=getattr(c, "norm_offset", 1.0), rows=want)
-        cap = c.logit_softcap
+        ops.norm_rows(x, c.final_norm, c.eps, xn, w_offset=getattr(c, "norm_offset", 1.0), rows=want,
+                      center=getattr(c, "norm_center", False))
+        cap, mul = c.logit_softcap, float(getattr(c, "logit_scale", 1.0))
+        if not cap and mul != 1.0:        # a design whose logits are the head's product times a constant
+            return ops.linear(xn, c.head, epi=EPI_SCALE, epi_param=mul)
         return ops.linear(xn, c.head, epi=EPI_SOFTCAP if cap else EPI_NONE, epi_param=cap or 0.0)
 
     # ------------------------------------------------------------------ one request

@@ -14,6 +14,17 @@ all their output projections another), the parts of a `SharedInputLayer`:
   feed-forwards  FUSED_FEEDFORWARDS["dense"] -> ClampedGLU
   layer          SharedInputLayer: n = norm(x); x += sum of the parts' outputs
 
+and, for pre-norm layers with a layer norm before each sublayer and a scale vector on each branch:
+
+  mixers         SCALED_MIXERS["latent_attention"] -> LatentAttention without a query latent, rotation in pairs
+                                                       (2i, 2i + 1), YaRN-scaled frequencies, a window, an output gate
+                 SCALED_MIXERS["mamba2"]           -> StateSpaceMixer (convolution + matrix state with a step size)
+  feed-forwards  SCALED_FEEDFORWARDS["dense"]      -> GatedDense (silu-gated unit)
+                 SCALED_FEEDFORWARDS["moe"]        -> GroupedExpertMixture (sigmoid scores with a selection bias, the
+                                                       choice limited to the best groups, clamped gated experts, a shared
+                                                       expert with a gate per token)
+  layer          ScaledPreNormLayer: x += s1 * mixer(LN(x)); x += s2 * ff(LN(x))
+
 A block declares `manifest(prefix)` (packed name, shape) and `pack(prefix, checkpoint tensors, arena)`; the model
 packs all blocks into ONE device arena (the layout the other models of this package use).  `forward(ctx, x)`
 enqueues the block's kernels; `ctx` carries the per-token slot / position arrays of the step and the cache pool,
@@ -48,10 +59,10 @@ class StepCtx:
             self._seq = self.ops.seq_tables(self.segments, self.pos.shape[0])
         return self._seq
 
-    def rope(self, base: float, dims: int) -> torch.Tensor:
-        key = (float(base), int(dims))
+    def rope(self, base: float, dims: int, scaling: Optional[tuple] = None) -> torch.Tensor:
+        key = (float(base), int(dims), scaling)
         if key not in self._rope:
-            self._rope[key] = self.ops.rope_table(self.pos, base, dims)
+            self._rope[key] = self.ops.rope_table(self.pos, base, dims, scaling)
         return self._rope[key]
 
 
@@ -61,16 +72,31 @@ class LatentAttention:
     q = W_uq rmsnorm(W_dq h);  [c | r] = W_dkv h, c rms-normed, r rotated: the cache row of the token;
     per head  k = [W_uk c | r],  v = W_uv c;  softmax(scale * q.k) over the causal prefix;  W_o on the heads.
     `kv_from = j`: no W_dkv, the rows that layer j cached are read instead (same rank and rotation).
-    The rotation is rotate-half on the first `rot_dims` of the rotated part, frequency base `rot_base`."""
+    The rotation is on the first `rot_dims` of the rotated part, frequency base `rot_base`; its pairs are
+    (i, i + rot_dims / 2) (`rotation="half"`) or (2i, 2i + 1) (`rotation="pairs"`); `rot.scaling` (factor, original,
+    fast, slow) rescales the frequencies by the YaRN rule and cos / sin by 0.1 ln(factor) + 1.
+    Without `q_rank` there is no query latent: q = W_q h.  `mask.size = w`: a query at position p sees the keys
+    p - w + 1 .. p.  `gated`: the heads' outputs are multiplied by sigmoid(W_g h) before W_o."""
 
-    def __init__(self, index: int, cfg: dict, width: int):
+    def __init__(self, index: int, cfg: dict, width: int, rotation: str = "half", gated: bool = False):
         self.index, self.W = index, width
         self.H, self.dim, self.rot_dim, self.vdim = cfg["heads"], cfg["dim"], cfg["rot_dim"], cfg["vdim"]
-        self.kv_rank, self.q_rank, self.scale = cfg["kv_rank"], cfg["q_rank"], float(cfg["scale"])
+        self.kv_rank, self.q_rank, self.scale = cfg["kv_rank"], int(cfg.get("q_rank") or 0), float(cfg["scale"])
         rot = cfg.get("rot") or {}
         self.rot_base, self.rot_dims = float(rot.get("base", 10000.0)), int(rot.get("dims", self.rot_dim))
+        sc = rot.get("scaling")
+        self.rot_scaling = None if not sc else (float(sc["factor"]), float(sc["original"]), float(sc["fast"]),
+                                                float(sc["slow"]))
+        if rotation not in ("half", "pairs"):
+            raise ValueError(f"layer {index}: rotation {rotation!r} (have 'half', 'pairs')")
+        self.pairs, self.gated = rotation == "pairs", bool(gated)
+        self.window = int((cfg.get("mask") or {}).get("size", 0))
         self.kv_from: Optional[int] = cfg.get("kv_from")
+        if not self.q_rank and self.kv_from is not None:
+            raise ValueError(f"layer {index}: a layer that borrows its latent needs a query latent")
+        self.n_q = self.H * (self.dim + self.rot_dim)
         self.cache_index = -1     # set by the model: which caching layer of the pool this mixer reads (and writes)
+        self.kv_dim, self.state_floats, self.state_off = self.kv_rank + self.rot_dim, 0, 0
         self.w: Dict[str, torch.Tensor] = {}
 
     @property
@@ -82,23 +108,45 @@ class LatentAttention:
         return self.kv_rank + self.rot_dim
 
     def manifest(self, p: str):
-        n_down = self.q_rank + (self.row_dim if self.own_kv else 0)
-        out = [(p + "down", (n_down, self.W)), (p + "dq.norm", (self.q_rank,)),
-               (p + "uq", (self.H * (self.dim + self.rot_dim), self.q_rank)),
-               (p + "ukT", (self.H, self.kv_rank, self.dim)), (p + "uv", (self.H * self.vdim, self.kv_rank)),
-               (p + "o", (self.W, self.H * self.vdim))]
+        # `down`: every product that reads the layer's input, stacked: [query latent, or the queries themselves |
+        # kv latent, rotated key part | gate]
+        n_down = (self.q_rank or self.n_q) + (self.row_dim if self.own_kv else 0) + (self.H * self.vdim if self.gated else 0)
+        out = [(p + "down", (n_down, self.W))]
+        if self.q_rank:
+            out += [(p + "dq.norm", (self.q_rank,)), (p + "uq", (self.n_q, self.q_rank))]
+        out += [(p + "ukT", (self.H, self.kv_rank, self.dim)), (p + "uv", (self.H * self.vdim, self.kv_rank)),
+                (p + "o", (self.W, self.H * self.vdim))]
         if self.own_kv:
             out.append((p + "dkv.norm", (self.kv_rank,)))
         return out
 
-    def pack(self, p: str, ck: Dict[str, torch.Tensor], view):
-        """ck: checkpoint tensors '<p>dq', '<p>dq.norm', '<p>uq', '<p>dkv', '<p>dkv.norm', '<p>uk', '<p>uv', '<p>o'"""
-        down = view(p + "down")
-        down[:self.q_rank].copy_(ck[p + "dq"])
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        """checkpoint name -> shape of everything this mixer reads"""
+        out = {p + "uk": (self.H * self.dim, self.kv_rank), p + "uv": (self.H * self.vdim, self.kv_rank),
+               p + "o": (self.W, self.H * self.vdim)}
+        if self.q_rank:
+            out.update({p + "dq": (self.q_rank, self.W), p + "dq.norm": (self.q_rank,), p + "uq": (self.n_q, self.q_rank)})
+        else:
+            out[p + "q"] = (self.n_q, self.W)
         if self.own_kv:
-            down[self.q_rank:].copy_(ck[p + "dkv"])          # one product for both down-projections
+            out.update({p + "dkv": (self.row_dim, self.W), p + "dkv.norm": (self.kv_rank,)})
+        if self.gated:
+            out[p + "g"] = (self.H * self.vdim, self.W)
+        return out
+
+    def pack(self, p: str, ck: Dict[str, torch.Tensor], view):
+        """ck: checkpoint tensors '<p>dq', '<p>dq.norm', '<p>uq' (or '<p>q'), '<p>dkv', '<p>dkv.norm', '<p>uk', '<p>uv',
+        '<p>o' (and '<p>g')"""
+        down = view(p + "down")
+        at = self.q_rank or self.n_q
+        down[:at].copy_(ck[p + "dq"] if self.q_rank else ck[p + "q"])
+        if self.own_kv:
+            down[at:at + self.row_dim].copy_(ck[p + "dkv"])  # one product for everything that reads the input
             view(p + "dkv.norm").copy_(ck[p + "dkv.norm"])
-        for n in ("dq.norm", "uq", "uv", "o"):
+            at += self.row_dim
+        if self.gated:
+            down[at:].copy_(ck[p + "g"])
+        for n in (("dq.norm", "uq") if self.q_rank else ()) + ("uv", "o"):
             view(p + n).copy_(ck[p + n])
         # the key up-projection per head, transposed: it is applied to the QUERY (absorbed form)
         view(p + "ukT").copy_(ck[p + "uk"].view(self.H, self.dim, self.kv_rank).transpose(1, 2))
@@ -113,11 +161,18 @@ class LatentAttention:
         Dl = r + dr
         D = ops.linear(x, w["down"])
         cache_layer = ctx.pool.buf[self.cache_index][..., :Dl]    # a pool row may be wider than this layer's
-        cs = ctx.rope(self.rot_base, self.rot_dims)
-        cq = ops.empty((T, self.q_rank))
-        ops.latent_post(D, w["dq.norm"], w.get("dkv.norm"), ctx.eps, cq, cache_layer if self.own_kv else None,
-                        ctx.slot, ctx.pos, cs, self.q_rank, r, dr, self.rot_dims)
-        q = ops.linear(cq, w["uq"])
+        cs = ctx.rope(self.rot_base, self.rot_dims, self.rot_scaling)
+        if self.q_rank:
+            cq = ops.empty((T, self.q_rank))
+            ops.latent_post(D, w["dq.norm"], w.get("dkv.norm"), ctx.eps, cq, cache_layer if self.own_kv else None,
+                            ctx.slot, ctx.pos, cs, self.q_rank, r, dr, self.rot_dims, pairs=self.pairs)
+            q = ops.linear(cq, w["uq"])
+            n_read = self.q_rank + (Dl if self.own_kv else 0)
+        else:             # the queries come straight from the input: the first columns of D
+            ops.latent_post(D[:, self.n_q:], None, w["dkv.norm"], ctx.eps, None, cache_layer, ctx.slot, ctx.pos, cs, 0, r,
+                            dr, self.rot_dims, pairs=self.pairs)
+            q = D[:, :self.n_q]
+            n_read = self.n_q + Dl
         qa = ops.empty((T, H * Dl))
         heads_tc = ops.tc_ok(T, dn, dn + dr, r) and dn % 64 == 0 and r % 64 == 0 and Dl % 4 == 0 and dv % 4 == 0
         if heads_tc:     # a prompt: the heads' products as ONE tcgen05 launch (inner sizes are whole k-blocks)
@@ -130,7 +185,7 @@ class LatentAttention:
                 heads_tc = False
         if not heads_tc:
             ops.gemm(q, w["ukT"], qa, M=T, N_=r, K=dn, xb=dn + dr, ldw=dn, wb=r * dn, yb=Dl, batch=H)
-        ops.rope_q(q, qa, cs, H, dn, dr, self.rot_dims, r)
+        ops.rope_q(q, qa, cs, H, dn, dr, self.rot_dims, r, pairs=self.pairs)
         ol = ops.empty((T, H * r))
         segs = ctx.segments or []
         done = False
@@ -139,14 +194,16 @@ class LatentAttention:
                 for start, n, slot, p0 in segs:      # long portions on the tensor cores, the rest on the row kernel
                     sl = slice(start, start + n)
                     if ops.tc_ok(n, Dl, r, cache_layer.stride(1)):
-                        self._attend_prompt(ops, qa[sl], cache_layer[slot], ctx.pos[sl], ol[sl], p0 + n)
+                        self._attend_prompt(ops, qa[sl], cache_layer[slot], ctx.pos[sl], ol[sl], p0, n)
                     else:
-                        ops.latent_attention(qa[sl], cache_layer, ctx.slot[sl], ctx.pos[sl], ol[sl], H, r, self.scale)
+                        ops.latent_attention(qa[sl], cache_layer, ctx.slot[sl], ctx.pos[sl], ol[sl], H, r, self.scale,
+                                             n_split=1, window=self.window)
                 done = True
             except _B200Error as e:
                 ops.tc_refused(e)
         if not done:
-            ops.latent_attention(qa, cache_layer, ctx.slot, ctx.pos, ol, H, r, self.scale)
+            ops.latent_attention(qa, cache_layer, ctx.slot, ctx.pos, ol, H, r, self.scale, window=self.window,
+                                 n_split=1 if ctx.segments is not None and T > 16 else None)
         att = ops.empty((T, H * dv))
         if heads_tc:
             try:
@@ -157,25 +214,45 @@ class LatentAttention:
                 heads_tc = False
         if not heads_tc:
             ops.gemm(ol, w["uv"], att, M=T, N_=dv, K=r, xb=r, ldw=r, wb=dv * r, yb=dv, batch=H)
+        if self.gated:       # the gate reads the layer's input like the projections: the last columns of D
+            ops.head_post(att, att, dv=dv, gate=D[:, n_read:])
         return ops.linear(att, w["o"])
 
 
-    def _attend_prompt(self, ops: LayerOps, qa, rows, pos, ol, S: int):
-        """A portion of a prompt against the S cached rows of its slot as two tcgen05 products: the cache rows are
-        the weight-major operand of the scores (absorbed queries x rows), the causal softmax runs in fp32 over the
-        score rows, and the transposed latent columns are the operand of the weighted sum.  Queries are taken in
-        chunks that bound the score buffer."""
+    def _attend_prompt(self, ops: LayerOps, qa, rows, pos, ol, p0: int, n: int):
+        """A portion of a prompt (positions p0 .. p0 + n - 1) against the cached rows of its slot as two tcgen05
+        products: the cache rows are the weight-major operand of the scores (absorbed queries x rows), the softmax
+        over the visible keys runs in fp32 over the score rows, and the transposed latent columns are the operand of
+        the weighted sum.  Queries are taken in chunks that bound the score buffer; with a window a chunk is about a
+        window long and meets only the rows from its first query's first visible key on."""
         H, r, Dl = self.H, self.kv_rank, self.kv_rank + self.rot_dim
-        n, Sp = qa.shape[0], (S + 63) // 64 * 64
-        ct = ops.cache_transpose(rows, S, Sp, r)
-        step = max(1, min(n, (1 << 27) // (H * Sp)))
+        if not self.window:
+            S = p0 + n
+            Sp = (S + 63) // 64 * 64
+            ct = ops.cache_transpose(rows, S, Sp, r)
+            step = max(1, min(n, (1 << 27) // (H * Sp)))
+            for a in range(0, n, step):
+                m = min(step, n - a)
+                qb = ops.to_bf16(qa[a:a + m].view(m * H, Dl), Dl)
+                sc = ops.empty((m * H, S))
+                ops.tc_gemm(qb, rows, sc, N_=S, K=Dl, ldw=rows.stride(0))
+                P = ops.empty((m * H, Sp), torch.bfloat16)
+                ops.masked_softmax_bf16(sc, pos[a:a + m], H, self.scale, P)
+                ops.tc_gemm(P, ct, ol[a:a + m].view(m * H, r), N_=r, K=Sp)
+            return
+        step = max(128, min(self.window, (1 << 27) // (H * 2 * self.window)))
+        step = -(-n // -(-n // step))          # equal chunks: no short one at the end
         for a in range(0, n, step):
             m = min(step, n - a)
+            key0 = max(p0 + a - self.window + 1, 0)
+            S = p0 + a + m - key0
+            Sp = (S + 63) // 64 * 64
+            ct = ops.cache_transpose(rows[key0:], S, Sp, r)
             qb = ops.to_bf16(qa[a:a + m].view(m * H, Dl), Dl)
             sc = ops.empty((m * H, S))
-            ops.tc_gemm(qb, rows, sc, N_=S, K=Dl, ldw=rows.stride(0))
+            ops.tc_gemm(qb, rows[key0:], sc, N_=S, K=Dl, ldw=rows.stride(0))
             P = ops.empty((m * H, Sp), torch.bfloat16)
-            ops.masked_softmax_bf16(sc, pos[a:a + m], H, self.scale, P)
+            ops.sink_softmax_bf16(sc, pos[a:a + m], H, None, self.scale, 0, self.window, key0, P)
             ops.tc_gemm(P, ct, ol[a:a + m].view(m * H, r), N_=r, K=Sp)
 
 
@@ -644,6 +721,259 @@ class SharedInputLayer:
             kv_base += 1 if part.kv_dim else 0
             state_base += part.state_floats
         ops.linear(cat, self.w["out"], out=x, add=True)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Pre-norm layers with a scale vector on each branch.  A mixer of such a layer has `forward(ctx, n) -> rows (T, width)`,
+# `kv_dim` (numbers it caches per token; the model sets `cache_index`) and `state_floats` (fp32 numbers it keeps per
+# slot; the model sets `state_off`); a feed-forward has `forward(ctx, n) -> keyword arguments of ops.residual_rows`.
+class StateSpaceMixer:
+    """Mamba-2 style state-space mixer (Dao and Gu, "Transformers are SSMs").  inner = heads * vdim, N = state, G = groups.
+    W_in n = [z: inner | x: inner | B: G N | C: G N | dt: heads]; x, B, C pass a causal convolution per channel (`conv`
+    taps, with bias; the slot keeps the last taps - 1 inputs) and silu; dt <- softplus(dt + dt_bias); per head h (group
+    h // (heads / G)):  S <- exp(-exp(A_log_h) dt) S + dt B x^T  (S: N x vdim, fp32 in the slot, zero at position 0),
+    y = S^T C + D_h x;  y <- y * silu(z), RMS-normed in `norm_groups` equal parts, times `norm`; then W_o."""
+
+    def __init__(self, index: int, cfg: dict, width: int):
+        self.index, self.W = index, width
+        self.H, self.vdim, self.N = int(cfg["heads"]), int(cfg["vdim"]), int(cfg["state"])
+        self.G, self.NG, self.taps = int(cfg.get("groups", 1)), int(cfg.get("norm_groups", 1)), int(cfg.get("conv") or 1)
+        self.inner = self.H * self.vdim
+        if self.H % self.G or self.inner % self.NG:
+            raise ValueError(f"layer {index}: {self.H} heads in {self.G} groups, {self.inner} numbers in {self.NG} norm groups")
+        self.n_conv = self.inner + 2 * self.G * self.N
+        self.n_in = 2 * self.inner + 2 * self.G * self.N + self.H
+        self.kv_dim = 0
+        self.conv_floats = max(self.taps - 1, 0) * self.n_conv
+        self.state_floats = self.conv_floats + state_floats(self.H, self.N, self.vdim)
+        self.cache_index, self.state_off = -1, 0
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def manifest(self, p: str):
+        return [(p + "in", (self.n_in, self.W)), (p + "conv", (self.n_conv, self.taps)), (p + "conv.b", (self.n_conv,)),
+                (p + "dt_bias", (self.H,)), (p + "A_log", (self.H,)), (p + "D", (self.H,)), (p + "norm", (self.inner,)),
+                (p + "o", (self.W, self.inner))]
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        return dict(self.manifest(p))        # the packed layout is the checkpoint's
+
+    def pack(self, p: str, ck, view):
+        for n, _ in self.manifest(p):
+            view(n).copy_(ck[n])
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n[len(p):]: view(n) for n, _ in self.manifest(p)}
+
+    def forward(self, ctx: StepCtx, x: torch.Tensor) -> torch.Tensor:
+        ops, w, T = ctx.ops, self.w, x.shape[0]
+        inner, gn, nc = self.inner, self.G * self.N, self.n_conv
+        D = ops.linear(x, w["in"])
+        st, off = ctx.pool.state, self.state_off
+        c = ops.short_conv(D[:, inner:inner + nc], w["conv"], st[:, off:off + self.conv_floats], ctx, act=True,
+                           bias=w["conv.b"])
+        y = ops.empty((T, inner))
+        ops.linear_state(c[:, inner + gn:], c[:, inner:inner + gn], c[:, :inner], y,
+                         st[:, off + self.conv_floats:off + self.state_floats], ctx, H=self.H, rep=self.H // self.G,
+                         dim=self.N, vdim=self.vdim, a=D[:, inner + nc:], A_log=w["A_log"], dt_bias=w["dt_bias"],
+                         dt_in=True, skip=w["D"])
+        ops.head_post(y, y, dv=self.vdim, gate=D[:, :inner], gate_silu=True, w=w["norm"], eps=ctx.eps,
+                      span=inner // self.NG, gate_first=True)
+        return ops.linear(y, w["o"])
+
+
+class GatedDense:
+    """Gated feed-forward W_down (g sigmoid(alpha g) (u + offset)), g = min(W_gate n, limit), u = clamp(W_up n, +-limit);
+    without a limit, alpha = 1 and offset = 0 it is the silu-gated unit W_down (silu(W_gate n) * W_up n).  Gate and up
+    are one stacked product."""
+
+    def __init__(self, index: int, cfg: dict, width: int, clamped: bool = False, alpha: float = 1.702):
+        self.index, self.W, self.ff = index, width, int(cfg["ff"])
+        self.limit = float(cfg["limit"]) if clamped else float("inf")
+        self.alpha, self.offset = (alpha, 1.0) if clamped else (1.0, 0.0)
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def manifest(self, p: str):
+        return [(p + "gu", (2 * self.ff, self.W)), (p + "down", (self.W, self.ff))]
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        return {p + "gate": (self.ff, self.W), p + "up": (self.ff, self.W), p + "down": (self.W, self.ff)}
+
+    def pack(self, p: str, ck, view):
+        gu = view(p + "gu")
+        gu[:self.ff].copy_(ck[p + "gate"])
+        gu[self.ff:].copy_(ck[p + "up"])
+        view(p + "down").copy_(ck[p + "down"])
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n[len(p):]: view(n) for n, _ in self.manifest(p)}
+
+    def rows(self, ctx: StepCtx, x: torch.Tensor) -> torch.Tensor:
+        ops = ctx.ops
+        D = ops.linear(x, self.w["gu"])
+        hid = ops.empty((x.shape[0], self.ff))
+        ops.glu_clamp(D[:, :self.ff], D[:, self.ff:], self.limit, self.alpha, hid, up_offset=self.offset)
+        return ops.linear(hid, self.w["down"])
+
+    def forward(self, ctx: StepCtx, x: torch.Tensor) -> dict:
+        return {"y": self.rows(ctx, x)}
+
+
+class GroupedExpertMixture:
+    """`experts` clamped gated feed-forwards (GatedDense with a limit) of which a token uses `top`.  Scores
+    s = sigmoid(W_router n) in fp32; the choice is made on s + `correction` among the experts of the `groups.keep` best
+    of `groups.count` equal groups of neighbours (a group's score: the sum of its two largest s + correction); the
+    weights are the chosen s over their sum.  `shared`: one more such unit that every token uses, times
+    sigmoid(W_sg n) (one number per token); its gate row rides at the end of the router's matrix."""
+
+    def __init__(self, index: int, cfg: dict, width: int, alpha: float = 1.702):
+        self.index, self.W, self.alpha = index, width, alpha
+        r = cfg["router"]
+        self.E, self.top, self.ff, self.limit = int(r["experts"]), int(r["top"]), int(cfg["expert"]["ff"]), float(cfg["expert"]["limit"])
+        g = r.get("groups") or {}
+        self.n_groups, self.keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
+        if self.E % self.n_groups or not 1 <= self.keep <= self.n_groups or self.top > self.keep * (self.E // self.n_groups):
+            raise ValueError(f"layer {index}: {self.E} experts in {self.n_groups} groups, {self.keep} kept, {self.top} chosen")
+        self.shared = GatedDense(index, cfg["shared"], width, clamped=True, alpha=alpha) if cfg.get("shared") else None
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def manifest(self, p: str):
+        out = [(p + "router", (self.E + (1 if self.shared else 0), self.W)), (p + "correction", (self.E,)),
+               (p + "gu", (self.E, 2 * self.ff, self.W)), (p + "down", (self.E, self.W, self.ff))]
+        return out + (self.shared.manifest(p + "shared.") if self.shared else [])
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        out = {p + "router": (self.E, self.W), p + "correction": (self.E,)}
+        for e in range(self.E):
+            out.update({p + f"e{e}.gate": (self.ff, self.W), p + f"e{e}.up": (self.ff, self.W), p + f"e{e}.down": (self.W, self.ff)})
+        if self.shared:
+            out.update(self.shared.checkpoint_tensors(p + "shared."))
+            out[p + "shared.sg"] = (1, self.W)
+        return out
+
+    def pack(self, p: str, ck, view):
+        router = view(p + "router")
+        router[:self.E].copy_(ck[p + "router"])
+        view(p + "correction").copy_(ck[p + "correction"])
+        gu, down = view(p + "gu"), view(p + "down")
+        for e in range(self.E):
+            gu[e, :self.ff].copy_(ck[p + f"e{e}.gate"])
+            gu[e, self.ff:].copy_(ck[p + f"e{e}.up"])
+            down[e].copy_(ck[p + f"e{e}.down"])
+        if self.shared:
+            router[self.E:].copy_(ck[p + "shared.sg"])
+            self.shared.pack(p + "shared.", ck, view)
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n: view(p + n) for n in ("router", "correction", "gu", "down")}
+        if self.shared:
+            self.shared.bind(p + "shared.", view)
+
+    def forward(self, ctx: StepCtx, x: torch.Tensor) -> dict:
+        ops, w, T, ff = ctx.ops, self.w, x.shape[0], self.ff
+        z = ops.linear(x, w["router"])
+        idx, wgt = ops.router_group_topk(z, self.top, w["correction"], self.n_groups, self.keep, E=self.E)
+        lists, count = ops.moe_group(idx, self.E)
+        out = None
+        if ops.tc_ok(T, self.W, ff):
+            try:
+                out = self._experts_prompt(ops, x, lists, count)
+            except _B200Error as e:
+                ops.tc_refused(e)
+        if out is None:
+            n_act = min(self.E, T * self.top)
+            hid = ops.empty((T * self.top, 2 * ff))
+            ops.gemm(x, w["gu"], hid, M=T, N_=2 * ff, K=self.W, wb=2 * ff * self.W, batch=self.E, lists=lists, count=count,
+                     x_div=self.top, compact=n_act)
+            act = ops.empty((T * self.top, ff))
+            ops.glu_clamp(hid[:, :ff], hid[:, ff:], self.limit, self.alpha, act)
+            out = ops.empty((T * self.top, self.W))
+            ops.gemm(act, w["down"], out, M=T, N_=self.W, K=ff, wb=self.W * ff, batch=self.E, lists=lists, count=count,
+                     x_div=1, compact=n_act)
+        res = {"y": out, "combine": wgt, "top": self.top}
+        if self.shared:
+            res.update(shared=self.shared.rows(ctx, x), shared_gate=z[:, self.E:])
+        return res
+
+    def _experts_prompt(self, ops: LayerOps, x, lists, count):
+        """A prompt step on the tensor cores (see ExpertMixture._experts_prompt): entries sorted by expert into
+        segments of whole token tiles, ONE grouped tcgen05 launch per projection — gate and up are one stacked
+        product —, the clamped activation between them."""
+        w, T, ff = self.w, x.shape[0], self.ff
+        n_all = T * self.top
+        order, group = ops.moe_tiles(lists, count, n_all)
+        n_rows = order.shape[0]
+        xs = ops.to_bf16(x, self.W, rows=n_rows, row_map=order, div=self.top)
+        hs = ops.empty((n_rows, 2 * ff))
+        ops.tc_gemm_grouped(xs, w["gu"], hs, group, N_=2 * ff, K=self.W, n_groups=self.E)
+        act = ops.empty((n_rows, ff))
+        ops.glu_clamp(hs[:, :ff], hs[:, ff:], self.limit, self.alpha, act)
+        ys = ops.empty((n_rows, self.W))
+        ops.tc_gemm_grouped(ops.to_bf16(act, ff), w["down"], ys, group, N_=self.W, K=ff, n_groups=self.E)
+        out = ops.empty((n_all, self.W))
+        ops.rows_scatter(ys, order, out, n_rows)
+        return out
+
+
+SCALED_MIXERS = {"latent_attention": lambda i, c, w: LatentAttention(i, c, w, rotation="pairs", gated=True),
+                 "mamba2": StateSpaceMixer}
+SCALED_FEEDFORWARDS = {"dense": GatedDense, "moe": GroupedExpertMixture}
+
+
+class ScaledPreNormLayer:
+    """x <- x + s1 * mixer(LN1(x));  x <- x + s2 * ff(LN2(x)),  LN(y) = (y - mean) / sqrt(var + eps) * w without bias,
+    s1, s2 vectors of the layer (`ls1`, `ls2`).  The residual stream and both updates are fp32."""
+
+    def __init__(self, index: int, cfg: dict, width: int):
+        self.index, self.W = index, width
+        if cfg["type"] not in SCALED_MIXERS:
+            raise ValueError(f"layer {index}: unknown mixer type {cfg['type']!r} (have {sorted(SCALED_MIXERS)})")
+        self.mixer = SCALED_MIXERS[cfg["type"]](index, cfg["mixer"], width)
+        f = cfg.get("mlp")
+        if f is not None and f.get("kind") not in SCALED_FEEDFORWARDS:
+            raise ValueError(f"layer {index}: unknown feed-forward kind {f.get('kind')!r} (have {sorted(SCALED_FEEDFORWARDS)})")
+        self.ff = None if f is None else SCALED_FEEDFORWARDS[f["kind"]](index, f, width)
+        self.kv_dim, self.state_floats = self.mixer.kv_dim, self.mixer.state_floats
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def _own(self):
+        return ["norm1", "ls1"] + (["norm2", "ls2"] if self.ff is not None else [])
+
+    def manifest(self, p: str):
+        out = [(p + n, (self.W,)) for n in self._own()] + self.mixer.manifest(p + "mix.")
+        return out + (self.ff.manifest(p + "mlp.") if self.ff is not None else [])
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        out = {p + n: (self.W,) for n in self._own()}
+        out.update(self.mixer.checkpoint_tensors(p + "mix."))
+        if self.ff is not None:
+            out.update(self.ff.checkpoint_tensors(p + "mlp."))
+        return out
+
+    def pack(self, p: str, ck, view):
+        for n in self._own():
+            view(p + n).copy_(ck[p + n])
+        self.mixer.pack(p + "mix.", ck, view)
+        if self.ff is not None:
+            self.ff.pack(p + "mlp.", ck, view)
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n: view(p + n) for n in self._own()}
+        self.mixer.bind(p + "mix.", view)
+        if self.ff is not None:
+            self.ff.bind(p + "mlp.", view)
+
+    def forward(self, ctx: StepCtx, x: torch.Tensor):
+        ops = ctx.ops
+        n = ops.empty(tuple(x.shape))
+        ops.norm_rows(x, self.w["norm1"], ctx.eps, n, center=True)
+        ops.residual_rows(self.mixer.forward(ctx, n), x, self.w["ls1"])
+        if self.ff is not None:
+            ops.norm_rows(x, self.w["norm2"], ctx.eps, n, center=True)
+            ops.residual_rows(x=x, ls=self.w["ls2"], **self.ff.forward(ctx, n))
 
 
 def assign_cache_layers(layers: List[PostNormLayer]) -> int:

@@ -15,7 +15,7 @@ import torch
 
 from .. import _native as N
 
-EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_ADD = 0, 1, 2, 3
+EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_ADD, EPI_SCALE = 0, 1, 2, 3, 4
 SM_COUNT = 148
 TC_MIN_ROWS = 128     # from this many rows on, a product of the bf16 serving mode runs on the tcgen05 GEMM
 WT_F32 = 3            # gemm_wt output mode: fp32 rows
@@ -81,48 +81,82 @@ class LayerOps:
                                         self.s), "lm_embed")
         return x
 
-    def inv_freq(self, base: float, dims: int) -> torch.Tensor:
-        """f_i = base^(-2i/dims), i < dims/2, computed in double precision on the host (once per rotation)"""
-        key = (float(base), int(dims))
+    def inv_freq(self, base: float, dims: int, scaling: Optional[tuple] = None) -> torch.Tensor:
+        """f_i = base^(-2i/dims), i < dims/2, computed in double precision on the host (once per rotation).
+        scaling = (factor, original, fast, slow), the YaRN rule (Peng et al., "YaRN: Efficient Context Window
+        Extension of Large Language Models"): with d(t) = dims ln(original / (2 pi t)) / (2 ln base) the index at
+        which a frequency makes t turns over `original` positions, lo = max(floor d(fast), 0),
+        hi = min(ceil d(slow), dims - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is
+        f_i (1 - r_i) + (f_i / factor) r_i."""
+        key = (float(base), int(dims), scaling)
         if key not in self._inv_freq:
-            f = np.power(np.float64(base), -2.0 * np.arange(dims // 2, dtype=np.float64) / dims)
+            half = dims // 2
+            f = np.power(np.float64(base), -2.0 * np.arange(half, dtype=np.float64) / dims)
+            if scaling is not None:
+                factor, original, fast, slow = (float(v) for v in scaling)
+
+                def index(turns):
+                    return dims * np.log(original / (2.0 * np.pi * turns)) / (2.0 * np.log(base))
+
+                lo, hi = max(np.floor(index(fast)), 0.0), min(np.ceil(index(slow)), dims - 1.0)
+                ramp = np.clip((np.arange(half, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+                f = f / factor * ramp + f * (1.0 - ramp)
             self._inv_freq[key] = self.to_device(f, np.float64)
         return self._inv_freq[key]
 
-    def rope_table(self, pos: torch.Tensor, base: float, dims: int) -> torch.Tensor:
+    @staticmethod
+    def rope_amplitude(scaling: Optional[tuple]) -> float:
+        """what a frequency scaling multiplies cos and sin by: 0.1 ln(factor) + 1"""
+        return 1.0 if scaling is None else 0.1 * float(np.log(float(scaling[0]))) + 1.0
+
+    def rope_table(self, pos: torch.Tensor, base: float, dims: int, scaling: Optional[tuple] = None) -> torch.Tensor:
         T, half = pos.shape[0], dims // 2
         if half == 0:             # nothing is rotated: the kernels never read the table
             return self.empty((1, 1, 2))
         cs = self.empty((T, half, 2))
-        self._ok(self.lib.b200_lm_rope_table(pos.data_ptr(), self.inv_freq(base, dims).data_ptr(), cs.data_ptr(), T,
-                                             half, self.s), "lm_rope_table")
+        self._ok(self.lib.b200_lm_rope_table(pos.data_ptr(), self.inv_freq(base, dims, scaling).data_ptr(), cs.data_ptr(),
+                                             T, half, self.rope_amplitude(scaling), self.s), "lm_rope_table")
         return cs
 
     def norm_rows(self, y: torch.Tensor, w: torch.Tensor, eps: float, x: torch.Tensor, *, w_offset: float = 0.0,
                   add: bool = False, combine: Optional[torch.Tensor] = None, top: int = 0,
-                  rows: Optional[torch.Tensor] = None):
-        """x (T, N) = or += rmsnorm(y rows) * (w_offset + w); `combine` (T, top): y holds `top` rows per token"""
+                  rows: Optional[torch.Tensor] = None, center: bool = False):
+        """x (T, N) = or += rmsnorm(y rows) * (w_offset + w); `combine` (T, top): y holds `top` rows per token;
+        center: the mean of the row is taken off first (a layer norm without bias)"""
         T, n = x.shape
         self._ok(self.lib.b200_lm_norm_rows(y.data_ptr(), y.stride(0), N.ptr(combine), int(top), w.data_ptr(),
                                             float(w_offset), float(eps), x.data_ptr(), x.stride(0), int(add),
-                                            N.ptr(rows), T, n, self.s), "lm_norm_rows")
+                                            N.ptr(rows), int(center), T, n, self.s), "lm_norm_rows")
 
-    def latent_post(self, D, wq, wkv, eps, cq, cache_layer, slot, pos, cs, q_rank, kv_rank, rot_dim, rot_dims):
-        """cache_layer: (slots, capacity, kv_rank + rot_dim) view of the pool, or None for a layer that borrows"""
+    def residual_rows(self, y: torch.Tensor, x: torch.Tensor, ls: Optional[torch.Tensor] = None, *,
+                      combine: Optional[torch.Tensor] = None, top: int = 0, shared: Optional[torch.Tensor] = None,
+                      shared_gate: Optional[torch.Tensor] = None):
+        """x (T, N) += ls * (y row, or the `combine`-weighted sum of `top` rows of y per token, + sigmoid(shared_gate)
+        * shared row): the residual update of a branch with a scale vector"""
+        T, n = x.shape
+        self._ok(self.lib.b200_lm_residual_rows(y.data_ptr(), y.stride(0), N.ptr(combine), int(top), N.ptr(shared),
+                                                shared.stride(0) if shared is not None else 0, N.ptr(shared_gate),
+                                                shared_gate.stride(0) if shared_gate is not None else 0, N.ptr(ls),
+                                                x.data_ptr(), x.stride(0), T, n, self.s), "lm_residual_rows")
+
+    def latent_post(self, D, wq, wkv, eps, cq, cache_layer, slot, pos, cs, q_rank, kv_rank, rot_dim, rot_dims,
+                    pairs: bool = False):
+        """cache_layer: (slots, capacity, kv_rank + rot_dim) view of the pool, or None for a layer that borrows;
+        q_rank 0: no query latent (wq, cq None; D's rows start with the kv latent); pairs: rotation pairs (2i, 2i+1)"""
         own = cache_layer is not None
         self._ok(self.lib.b200_lm_latent_post(
-            D.data_ptr(), D.stride(0), wq.data_ptr(), N.ptr(wkv), float(eps), cq.data_ptr(), cq.stride(0),
+            D.data_ptr(), D.stride(0), N.ptr(wq), N.ptr(wkv), float(eps), N.ptr(cq), cq.stride(0) if cq is not None else 0,
             N.ptr(cache_layer), int(own and cache_layer.dtype == torch.bfloat16),
             cache_layer.stride(0) if own else 0, cache_layer.stride(1) if own else 0, N.ptr(slot), N.ptr(pos),
-            N.ptr(cs), q_rank, kv_rank, rot_dim, rot_dims, int(own), D.shape[0], self.s), "lm_latent_post")
+            N.ptr(cs), q_rank, kv_rank, rot_dim, rot_dims, int(own), int(pairs), D.shape[0], self.s), "lm_latent_post")
 
-    def rope_q(self, q, qa, cs, H, dim, rot_dim, rot_dims, kv_rank):
+    def rope_q(self, q, qa, cs, H, dim, rot_dim, rot_dims, kv_rank, pairs: bool = False):
         T = q.shape[0]
         self._ok(self.lib.b200_lm_rope_q(q.data_ptr(), q.stride(0), dim + rot_dim, dim, qa.data_ptr(), qa.stride(0),
-                                         kv_rank + rot_dim, kv_rank, cs.data_ptr(), H, rot_dim, rot_dims, T, self.s),
-                 "lm_rope_q")
+                                         kv_rank + rot_dim, kv_rank, cs.data_ptr(), H, rot_dim, rot_dims, int(pairs), T,
+                                         self.s), "lm_rope_q")
 
-    def latent_attention(self, qa, cache_layer, slot, pos, out, H, kv_rank, scale, n_split=None):
+    def latent_attention(self, qa, cache_layer, slot, pos, out, H, kv_rank, scale, n_split=None, window: int = 0):
         """n_split: blocks per (token, head group) that share the keys (None: enough to fill the GPU when the
         step has few tokens — a decode step —, 1 for prompts)"""
         T, Dl = qa.shape[0], cache_layer.shape[-1]
@@ -133,13 +167,25 @@ class LayerOps:
         self._ok(self.lib.b200_lm_latent_attention(
             qa.data_ptr(), qa.stride(0), cache_layer.data_ptr(), int(cache_layer.dtype == torch.bfloat16),
             cache_layer.stride(0), cache_layer.stride(1), slot.data_ptr(), pos.data_ptr(), out.data_ptr(),
-            out.stride(0), H, Dl, kv_rank, float(scale), 0, N.ptr(part), n_split, T, self.s), "lm_latent_attention")
+            out.stride(0), H, Dl, kv_rank, float(scale), 0, int(window), N.ptr(part), n_split, T, self.s),
+            "lm_latent_attention")
 
     def router_topk(self, z, top):
         T, E = z.shape
         idx, wgt = self.empty((T, top), torch.int32), self.empty((T, top))
         self._ok(self.lib.b200_lm_router_topk(z.data_ptr(), z.stride(0), E, top, idx.data_ptr(), wgt.data_ptr(), T,
                                               self.s), "lm_router_topk")
+        return idx, wgt
+
+    def router_group_topk(self, z, top, correction=None, n_groups: int = 1, keep: int = 1, E: Optional[int] = None):
+        """sigmoid scores; choice on score + correction among the experts of the `keep` best of `n_groups` groups;
+        weights = the chosen scores over their sum.  z may hold more columns than experts (E of them are read)"""
+        T = z.shape[0]
+        E = z.shape[1] if E is None else E
+        idx, wgt = self.empty((T, top), torch.int32), self.empty((T, top))
+        self._ok(self.lib.b200_lm_router_group_topk(z.data_ptr(), z.stride(0), N.ptr(correction), E, top, int(n_groups),
+                                                    int(keep), idx.data_ptr(), wgt.data_ptr(), T, self.s),
+                 "lm_router_group_topk")
         return idx, wgt
 
     def moe_group(self, idx, E):
@@ -275,7 +321,8 @@ class LayerOps:
         both = self.to_device(np.concatenate([first, seqs.reshape(-1)]))
         return both[:T], both[T:].view(len(segments), 2), len(segments)
 
-    def short_conv(self, U: torch.Tensor, w: torch.Tensor, state: torch.Tensor, ctx, act: bool = False) -> torch.Tensor:
+    def short_conv(self, U: torch.Tensor, w: torch.Tensor, state: torch.Tensor, ctx, act: bool = False,
+                   bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """U (T, C) column range of projected rows; w (C, taps); state (slots, >= (taps-1) * C) fp32 view of the pool"""
         T, C = U.shape
         first, seqs, G = ctx.seq_tables()
@@ -283,7 +330,8 @@ class LayerOps:
         self._ok(self.lib.b200_lm_short_conv(U.data_ptr(), U.stride(0), w.data_ptr(), Y.data_ptr(), Y.stride(0),
                                              state.data_ptr() if state.numel() else 0, state.stride(0), ctx.slot.data_ptr(),
                                              ctx.pos.data_ptr(),
-                                             first.data_ptr(), seqs.data_ptr(), G, C, w.shape[1], int(act), T, self.s),
+                                             first.data_ptr(), seqs.data_ptr(), G, C, w.shape[1], int(act), N.ptr(bias), T,
+                                             self.s),
                  "lm_short_conv")
         return Y
 
@@ -323,7 +371,8 @@ class LayerOps:
                                                     S.shape[0], P.shape[1], self.s), "lm_sink_softmax_bf16")
 
     def linear_state(self, q, k, v, out, state, ctx, *, H, rep, dim, vdim, act=False, unit_eps=0.0, q_scale=1.0,
-                     decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False):
+                     decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False, dt_in=False, skip=None):
+        """dt_in: the state-space form, u = softplus(a + dt_bias) v; skip (H,): out += skip[h] v"""
         _, seqs, G = ctx.seq_tables()
         T, Hk = q.shape[0], H // rep
         # a prompt step does the per-token work (activation, unit lengths, k . q, decay, beta) in one parallel pass first
@@ -332,21 +381,25 @@ class LayerOps:
             q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
             state.data_ptr(), state.stride(0), seqs.data_ptr(), G, ctx.slot.data_ptr(), ctx.pos.data_ptr(), H, rep, dim,
             vdim, int(act), float(unit_eps), float(q_scale), N.ptr(decay_const), N.ptr(a), a.stride(0) if a is not None else 0,
-            N.ptr(A_log), N.ptr(dt_bias), N.ptr(b), b.stride(0) if b is not None else 0, int(delta), N.ptr(prep), T, self.s),
+            N.ptr(A_log), N.ptr(dt_bias), N.ptr(b), b.stride(0) if b is not None else 0, int(delta), int(dt_in), N.ptr(skip),
+            N.ptr(prep), T, self.s),
             "lm_linear_state")
 
     def head_post(self, o, out, *, dv, gate=None, gate_per_head=False, gate_silu=False, w=None, eps=0.0, span=0,
-                  scale=1.0):
+                  scale=1.0, gate_first=False):
         T, n = o.shape
         self._ok(self.lib.b200_lm_head_post(o.data_ptr(), o.stride(0), N.ptr(gate), gate.stride(0) if gate is not None else 0,
                                             N.ptr(w), w.numel() if w is not None else 0, float(eps), int(span),
                                             int(gate_per_head), int(gate_silu), dv, n, float(scale), out.data_ptr(),
-                                            out.stride(0), T, self.s), "lm_head_post")
+                                            out.stride(0), int(gate_first), T, self.s), "lm_head_post")
 
-    def glu_clamp(self, G, U, limit, alpha, Y):
+    def glu_clamp(self, G, U, limit, alpha, Y, up_offset: float = 1.0):
+        """Y = g sigmoid(alpha g) (u + up_offset), g = min(G, limit), u = clamp(U, +-limit); limit inf, alpha 1 and
+        up_offset 0 give the plain silu-gated unit"""
         T, n = G.shape
         self._ok(self.lib.b200_lm_glu_clamp(G.data_ptr(), G.stride(0), U.data_ptr(), U.stride(0), float(limit),
-                                            float(alpha), Y.data_ptr(), Y.stride(0), n, T, self.s), "lm_glu_clamp")
+                                            float(alpha), float(up_offset), Y.data_ptr(), Y.stride(0), n, T, self.s),
+                 "lm_glu_clamp")
 
     def argmax_rows(self, z, tok, logprob=None):
         B, V = z.shape
