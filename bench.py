@@ -511,9 +511,11 @@ def c4_leg(dev, args):
 
 
 # ------------------------------------------------------------------------------------------------------------
-# `--design buzopel | sonulorn`: prefill and decode throughput of a decoder design assembled from decoder_blocks
+# `--design buzopel | sonulorn | lilosun`: prefill and decode throughput of a decoder design assembled from decoder_blocks
 # over the layer ops (Buzopel: latent attention + expert mixture; Sonulorn: sink attention, matrix-state mixers and a
-# clamped gated feed-forward behind one shared input projection) at sizes that resemble real layers, beside the closest
+# clamped gated feed-forward behind one shared input projection; Lilosun: windowed gated latent attention and state-space
+# mixers in scaled pre-norm layers with a grouped expert mixture — also beside Buzopel, the closest design on the same
+# engine, at equal width, heads, ranks, experts and expert size) at sizes that resemble real layers, beside the closest
 # existing model of the package — the Qwen2-VL language model (dense GQA decoder on the native engine) — at equal
 # width, depth, head count and ACTIVE feed-forward size.  Random weights; inputs are token ids resident on the host;
 # CUDA events on the engine's stream; the weights of either model (>= 1 GB) exceed the L2.
@@ -597,8 +599,96 @@ def _sonulorn_account(m, z, T):
     return act_w, other, mix_flops
 
 
-DESIGNS = {"buzopel": (DESIGN_SIZES, _buzopel_model, _buzopel_account),
-           "sonulorn": (SONULORN_SIZES, _sonulorn_model, _sonulorn_account)}
+LILOSUN_SIZES = {
+    "2048w": dict(width=2048, layers=4, heads=16, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, window=1024,
+                  ssm_heads=64, ssm_vdim=64, state=128, groups=8, experts=64, top=6, ff=1408, expert_groups=8, keep=4,
+                  shared_ff=2816, dense_ff=8448, vocab=32000),
+    "4096w": dict(width=4096, layers=4, heads=32, dim=128, rot=64, vdim=128, kv_rank=512, q_rank=1536, window=1024,
+                  ssm_heads=128, ssm_vdim=64, state=128, groups=8, experts=64, top=8, ff=2048, expert_groups=8, keep=4,
+                  shared_ff=4096, dense_ff=16384, vocab=32000),
+}
+
+
+def _lilosun_config(z):
+    att = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+           "mask": {"size": z["window"]}, "scale": 1.0 / float(z["dim"] + z["rot"]) ** 0.5,
+           "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    ssm = {"heads": z["ssm_heads"], "vdim": z["ssm_vdim"], "state": z["state"], "groups": z["groups"],
+           "norm_groups": z["groups"], "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0}, "shared": {"ff": z["shared_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["expert_groups"], "keep": z["keep"]}}}
+    layers = [{"type": "latent_attention", "mixer": att, "mlp": {"kind": "dense", "ff": z["dense_ff"]}},
+              {"type": "mamba2", "mixer": ssm, "mlp": moe}, {"type": "latent_attention", "mixer": att, "mlp": moe},
+              {"type": "mamba2", "mixer": ssm, "mlp": moe}]
+    return {"architecture": "Lilosun", "vocab": z["vocab"], "width": z["width"], "layers": layers[:z["layers"]],
+            "norm": {"eps": 1e-5}, "logit_scale": 0.5}
+
+
+def _lilosun_model(z, dev):
+    from mlx_vlm_b200.models.lilosun import Model as LModel, ModelConfig as LConfig
+    return LModel(LConfig.from_dict(_lilosun_config(z)), device=dev).init_random(0)
+
+
+def _lilosun_account(m, z, T):
+    from mlx_vlm_b200.models.decoder_blocks import GatedDense, LatentAttention
+    W = z["width"]
+    act_w, other, mix_flops = 0, 8 * m.state_floats, 0.0      # the fp32 state is read and written once per token
+    for L in m.layers:
+        x = L.mixer
+        if isinstance(x, LatentAttention):
+            act_w += x.w["down"].shape[0] * W + x.H * x.dim * x.kv_rank + x.H * x.vdim * x.kv_rank + W * x.H * x.vdim
+            # visible keys of a query, averaged over the prompt; a decoded token after it reads a whole window
+            mean_seen = sum(min(p + 1, x.window or p + 1) for p in range(T)) / T
+            mix_flops += 2 * x.H * (x.row_dim + x.kv_rank) * mean_seen
+            other += 2 * x.row_dim * min(x.window or T, T)
+        else:
+            act_w += x.n_in * W + W * x.inner
+            mix_flops += 4 * x.H * x.N * x.vdim
+        f = L.ff
+        if isinstance(f, GatedDense):
+            act_w += 3 * f.ff * W
+        elif f is not None:
+            act_w += f.w["router"].shape[0] * W + 3 * f.top * f.ff * W + (3 * f.shared.ff * W if f.shared else 0)
+    return act_w, other, mix_flops
+
+
+# design -> (sizes, model factory, byte / flop accounting, closest design on the same engine measured beside it or None)
+DESIGNS = {"buzopel": (DESIGN_SIZES, _buzopel_model, _buzopel_account, None),
+           "sonulorn": (SONULORN_SIZES, _sonulorn_model, _sonulorn_account, None),
+           "lilosun": (LILOSUN_SIZES, _lilosun_model, _lilosun_account, ("buzopel_equal_size", _buzopel_model, _buzopel_account))}
+
+
+def _measure_layered(m, account, z, T, n_dec, rows, ids, args, timed, hbm, tpk):
+    """prefill, single-request decode and lock-step decode of `rows` requests of a layer-assembled design"""
+    import torch
+    lm, eng = m.language_model, m.engine
+    state = {}
+
+    def b_prefill():
+        state["cache"] = lm.make_cache()
+        lm(ids, cache=state["cache"], logits_to_keep=1, reserve_tokens=T + n_dec * (args.warmup + args.steps + 2))
+
+    def b_decode():
+        lm.fused_greedy_decode_n(n_dec, state["cache"])
+
+    pre = timed(eng, b_prefill)
+    dec = timed(eng, b_decode) / n_dec
+    pool = lm.make_pool(rows, T + n_dec * (args.warmup + args.steps + 2) + 8)
+    caches = [lm.make_cache_row(pool, r) for r in range(rows)]
+    lm.prefill_rows([ids[0]] * rows, [None] * rows, caches)
+    eng.bind_pool(pool)
+    eng.batch_begin([1] * rows, [T] * rows, [T] * rows, [1] * rows)
+    bdec = timed(eng, lambda: eng.batch_decode(n_dec)) / n_dec
+    act_w, other_bytes, att_flops = account(m, z, T)
+    head_w = z["vocab"] * z["width"]
+    bytes_tok = 2 * (act_w + head_w) + other_bytes                     # what one decoded token has to move
+    flops_tok = 2 * (act_w + head_w / T)                               # prefill: the head runs on one row
+    return {"prefill_ms": pre, "prefill_tok_s": T / pre * 1e3, "decode_ms_per_token": dec,
+            "decode_tok_s": 1e3 / dec, "batch_decode_ms_per_step": bdec, "batch_decode_tok_s": rows / bdec * 1e3,
+            "active_weight_bytes_per_token": 2 * (act_w + head_w), "bytes_per_decoded_token": bytes_tok,
+            "decode_frac_of_hbm": bytes_tok / (dec / 1e3) / 1e9 / hbm,
+            "prefill_frac_of_tensor": (flops_tok + att_flops) * T / (pre / 1e3) / 1e12 / tpk,
+            "graph_replays": eng.graph_replays, "launches": eng.launch_count}
 
 
 def design_leg(dev, args):
@@ -608,7 +698,7 @@ def design_leg(dev, args):
     from mlx_vlm_b200.models.qwen2_vl.config import ModelConfig as QConfig, TextConfig, VisionConfig
     from mlx_vlm_b200.utils import load_synthetic
     T, n_dec, rows = args.design_prompt, args.design_out, args.design_rows
-    sizes, make_model, account = DESIGNS[args.design]
+    sizes, make_model, account, beside = DESIGNS[args.design]
     hbm, hbm_src = _peaks()
     tpk, tpk_src = _tensor_peak()
     out = {"prompt_tokens": T, "decode_tokens": n_dec, "rows": rows, "sizes": {}, "peaks": {"hbm_GBs": hbm, "hbm_source": hbm_src,
@@ -632,39 +722,13 @@ def design_leg(dev, args):
             continue
         ids = rng.integers(0, z["vocab"], size=(1, T))
         res = {}
-        # ---- the new design ------------------------------------------------------------------------------
-        m = make_model(z, dev)
-        lm, eng = m.language_model, m.engine
         state = {}
-
-        def b_prefill():
-            state["cache"] = lm.make_cache()
-            lm(ids, cache=state["cache"], logits_to_keep=1, reserve_tokens=T + n_dec * (args.warmup + args.steps + 2))
-
-        def b_decode():
-            lm.fused_greedy_decode_n(n_dec, state["cache"])
-
-        pre = timed(eng, b_prefill)
-        dec = timed(eng, b_decode) / n_dec
-        pool = lm.make_pool(rows, T + n_dec * (args.warmup + args.steps + 2) + 8)
-        caches = [lm.make_cache_row(pool, r) for r in range(rows)]
-        lm.prefill_rows([ids[0]] * rows, [None] * rows, caches)
-        eng.bind_pool(pool)
-        eng.batch_begin([1] * rows, [T] * rows, [T] * rows, [1] * rows)
-        bdec = timed(eng, lambda: eng.batch_decode(n_dec)) / n_dec
-        act_w, other_bytes, att_flops = account(m, z, T)
         head_w = z["vocab"] * z["width"]
-        bytes_tok = 2 * (act_w + head_w) + other_bytes                     # what one decoded token has to move
-        flops_tok = 2 * (act_w + head_w / T)                               # prefill: the head runs on one row
-        res[args.design] = {"prefill_ms": pre, "prefill_tok_s": T / pre * 1e3, "decode_ms_per_token": dec,
-                            "decode_tok_s": 1e3 / dec, "batch_decode_ms_per_step": bdec, "batch_decode_tok_s": rows / bdec * 1e3,
-                            "active_weight_bytes_per_token": 2 * (act_w + head_w), "bytes_per_decoded_token": bytes_tok,
-                            "decode_frac_of_hbm": bytes_tok / (dec / 1e3) / 1e9 / hbm,
-                            "prefill_frac_of_tensor": (flops_tok + att_flops) * T / (pre / 1e3) / 1e12 / tpk,
-                            "graph_replays": eng.graph_replays, "launches": eng.launch_count}
-        del m, lm, eng, pool, caches
-        state.clear()
-        torch.cuda.empty_cache()
+        # ---- the new design (and, if named, the closest design on the same engine at equal size) ----------
+        for label, make_model_, account_ in [(args.design, make_model, account)] + ([beside] if beside else []):
+            res[label] = _measure_layered(make_model_(z, dev), account_, z, T, n_dec, rows, ids, args, timed, hbm, tpk)
+            torch.cuda.empty_cache()
+
         # ---- the closest existing model at equal size ---------------------------------------------------------
         text = TextConfig(model_type="qwen2_vl", hidden_size=z["width"], num_hidden_layers=z["layers"],
                           intermediate_size=z["top"] * z["ff"], num_attention_heads=z["heads"], rms_norm_eps=1e-6,
@@ -722,7 +786,7 @@ def main():
     ap.add_argument("--no-mega", action="store_true")
     ap.add_argument("--mega-mode", type=int, default=None,
                     help="decode kernel: 0 per-phase kernels, 1 k_mega (CUDA cores), 2 k_mega_tc (tcgen05)")
-    ap.add_argument("--design", default=None, choices=["buzopel", "sonulorn"],
+    ap.add_argument("--design", default=None, choices=["buzopel", "sonulorn", "lilosun"],
                     help="instead of the default workload: prefill / decode throughput of this decoder design at "
                          "layer sizes of real models, beside the closest existing model at equal size")
     ap.add_argument("--design-sizes", default="", help="comma-separated subset of the sizes (default: all)")

@@ -81,6 +81,17 @@ def window_visible(T: int, window: Optional[int]) -> torch.Tensor:
     return ok
 
 
+def window_attention(q, k, v, scale: float, window: Optional[int]) -> torch.Tensor:
+    """q, k (T, H, D), v (T, H, dv), token t at position t: softmax over the visible keys of scale * q . k, times v"""
+    T, H, _ = q.shape
+    ok = window_visible(T, window)
+    out = torch.zeros(T, H, v.shape[-1], dtype=q.dtype)
+    for a in range(H):
+        s = (q[:, a] @ k[:, a].T * scale).masked_fill(~ok, float("-inf"))
+        out[:, a] = torch.softmax(s, dim=-1) @ v[:, a]
+    return out
+
+
 def latent_attention(h, W, p, m, eps, pos):
     """h (T, width) -> (T, width).  m: heads, dim, rot_dim, vdim, kv_rank, scale, rot, mask"""
     T = h.shape[0]
@@ -94,12 +105,8 @@ def latent_attention(h, W, p, m, eps, pos):
     k_rot = rotate_pairs(down[:, None, r:], pos, base, dims, scaling)[:, 0]         # one part for all heads
     k_plain = (c @ W[p + "uk"].T).view(T, H, d)
     v = (c @ W[p + "uv"].T).view(T, H, dv)
-    ok = window_visible(T, (m.get("mask") or {}).get("size"))
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
-    for a in range(H):
-        s = (q_plain[:, a] @ k_plain[:, a].T + q_rot[:, a] @ k_rot.T) * float(m["scale"])
-        s = s.masked_fill(~ok, float("-inf"))
-        out[:, a] = torch.softmax(s, dim=-1) @ v[:, a]
+    k = torch.cat([k_plain, k_rot[:, None, :].expand(T, H, dr)], dim=-1)
+    out = window_attention(torch.cat([q_plain, q_rot], dim=-1), k, v, float(m["scale"]), (m.get("mask") or {}).get("size"))
     gated = out.reshape(T, H * dv) * torch.sigmoid(h @ W[p + "g"].T)
     return gated @ W[p + "o"].T
 
