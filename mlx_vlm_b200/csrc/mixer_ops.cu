@@ -528,14 +528,15 @@ struct HeadPostP {
   float scale;
   float* out; long ldo;
   int gate_first;                  // the gate multiplies o BEFORE the norm (the mean square is that of the gated numbers)
-};
+  int wide;                        // a whole block per norm group (long groups, or few tokens: a step of one token
+};                                 // still spreads over many blocks) instead of a warp per group
 __global__ void head_post_kernel(HeadPostP p) {
   // a norm group of up to 1024 numbers belongs to one warp (blockIdx.y counts warps' worth of groups), a longer one
   // to a whole block (blockIdx.y = the group): a step of one token still spreads over many blocks
   __shared__ float red[32];
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int span = p.span > 0 ? p.span : p.dv, groups = p.n / span;
-  const bool wide = span > 1024;
+  const bool wide = p.wide != 0;
   const int gi = wide ? (int)blockIdx.y : (int)blockIdx.y * nw + warp;
   if (gi >= groups) return;                    // whole warps (or, wide, whole blocks) leave together
   const int me = wide ? threadIdx.x : lane, step = wide ? blockDim.x : 32;
@@ -605,6 +606,20 @@ __global__ void glu_clamp4_kernel(const float* __restrict__ G, long ldg, const f
     y[e] = g * sigmoid_exact(alpha * g) * (u + up_off);
   }
   *reinterpret_cast<float4*>(Y + (long)t * ldy + i) = make_float4(y[0], y[1], y[2], y[3]);
+}
+
+// the same, written as the bf16 operand rows of the next tensor-core product (zero-padded to Kp columns)
+__global__ void glu_clamp_bf16_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
+                                      float alpha, float up_off, bf16* __restrict__ Y, int n, int Kp) {
+  const long t = blockIdx.x;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < Kp; i += blockDim.x * gridDim.y) {
+    float y = 0.f;
+    if (i < n) {
+      const float g = fminf(G[t * ldg + i], lim), u = fminf(fmaxf(U[t * ldu + i], -lim), lim);
+      y = g * sigmoid_exact(alpha * g) * (u + up_off);
+    }
+    Y[t * Kp + i] = f2bf(y);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -790,9 +805,10 @@ int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, con
   B200_REQUIRE(o && out && T > 0 && n > 0 && dv > 0 && n % dv == 0, "lm_head_post: bad argument");
   B200_REQUIRE(span == 0 || n % span == 0, "lm_head_post: norm groups of %d numbers in rows of %d", span, n);
   B200_REQUIRE(!w || w_len > 0, "lm_head_post: a weight needs its length");
-  HeadPostP p{o, ldi, gate, ldg, (const bf16*)w, w_len, eps, span, gate_per_head, gate_silu, dv, n, scale, out, ldo, gate_first};
   const int grp = span > 0 ? span : dv, groups = n / grp;
-  head_post_kernel<<<dim3(T, grp > 1024 ? groups : cdiv(groups, 8)), 256, 0, (cudaStream_t)st>>>(p);
+  const int wide = grp > 1024 || (grp >= 256 && (long)T * groups <= 256);
+  HeadPostP p{o, ldi, gate, ldg, (const bf16*)w, w_len, eps, span, gate_per_head, gate_silu, dv, n, scale, out, ldo, gate_first, wide};
+  head_post_kernel<<<dim3(T, wide ? groups : cdiv(groups, 8)), 256, 0, (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
@@ -804,6 +820,14 @@ int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float 
                   (((uintptr_t)G | (uintptr_t)U | (uintptr_t)Y) & 15) == 0;
   if (v4 && T > 16) glu_clamp4_kernel<<<dim3(T, cdiv(n, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, Y, ldy, n);
   else glu_clamp_kernel<<<dim3(T, cdiv(n, 256)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, Y, ldy, n);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_glu_clamp_bf16(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
+                           void* Y, int n, int Kp, int T, void* st) {
+  B200_REQUIRE(G && U && Y && T > 0 && n > 0 && Kp >= n, "lm_glu_clamp_bf16: bad argument");
+  glu_clamp_bf16_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

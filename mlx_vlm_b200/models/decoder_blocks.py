@@ -812,9 +812,18 @@ class GatedDense:
     def rows(self, ctx: StepCtx, x: torch.Tensor) -> torch.Tensor:
         ops = ctx.ops
         D = ops.linear(x, self.w["gu"])
+        down = self.w["down"]
+        if ops.tc_ok(x.shape[0], self.ff, down.stride(0)) and down.data_ptr() % 16 == 0:
+            try:          # a prompt: the activation is written as the bf16 operand of the down product, in one pass
+                hb = ops.glu_clamp_bf16(D[:, :self.ff], D[:, self.ff:], self.limit, self.alpha, up_offset=self.offset)
+                y = ops.empty((x.shape[0], self.W))
+                ops.tc_gemm(hb, down, y, N_=self.W, K=self.ff, ldw=down.stride(0))
+                return y
+            except _B200Error as e:
+                ops.tc_refused(e)
         hid = ops.empty((x.shape[0], self.ff))
         ops.glu_clamp(D[:, :self.ff], D[:, self.ff:], self.limit, self.alpha, hid, up_offset=self.offset)
-        return ops.linear(hid, self.w["down"])
+        return ops.linear(hid, down)
 
     def forward(self, ctx: StepCtx, x: torch.Tensor) -> dict:
         return {"y": self.rows(ctx, x)}
@@ -908,10 +917,9 @@ class GroupedExpertMixture:
         xs = ops.to_bf16(x, self.W, rows=n_rows, row_map=order, div=self.top)
         hs = ops.empty((n_rows, 2 * ff))
         ops.tc_gemm_grouped(xs, w["gu"], hs, group, N_=2 * ff, K=self.W, n_groups=self.E)
-        act = ops.empty((n_rows, ff))
-        ops.glu_clamp(hs[:, :ff], hs[:, ff:], self.limit, self.alpha, act)
+        act = ops.glu_clamp_bf16(hs[:, :ff], hs[:, ff:], self.limit, self.alpha)      # activation and rounding in one pass
         ys = ops.empty((n_rows, self.W))
-        ops.tc_gemm_grouped(ops.to_bf16(act, ff), w["down"], ys, group, N_=self.W, K=ff, n_groups=self.E)
+        ops.tc_gemm_grouped(act, w["down"], ys, group, N_=self.W, K=ff, n_groups=self.E)
         out = ops.empty((n_all, self.W))
         ops.rows_scatter(ys, order, out, n_rows)
         return out

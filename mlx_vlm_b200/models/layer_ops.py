@@ -163,6 +163,8 @@ class LayerOps:
         if n_split is None:
             groups = T * ((H + 7) // 8)
             n_split = max(1, min(64, (2 * SM_COUNT) // groups))
+            if window > 0:       # a window holds at most this many key tiles (of 32): more splits would only be merged
+                n_split = min(n_split, (window + 31) // 32)
         part = self.empty((T, H, n_split, kv_rank + 2)) if n_split > 1 else None
         self._ok(self.lib.b200_lm_latent_attention(
             qa.data_ptr(), qa.stride(0), cache_layer.data_ptr(), int(cache_layer.dtype == torch.bfloat16),
@@ -400,6 +402,16 @@ class LayerOps:
         self._ok(self.lib.b200_lm_glu_clamp(G.data_ptr(), G.stride(0), U.data_ptr(), U.stride(0), float(limit),
                                             float(alpha), float(up_offset), Y.data_ptr(), Y.stride(0), n, T, self.s),
                  "lm_glu_clamp")
+
+    def glu_clamp_bf16(self, G, U, limit, alpha, up_offset: float = 1.0) -> torch.Tensor:
+        """the gated activation written as bf16 operand rows (T, ceil64(n)) of the next tensor-core product"""
+        T, n = G.shape
+        Kp = (n + 63) // 64 * 64
+        Y = self.empty((T, Kp), torch.bfloat16)
+        self._ok(self.lib.b200_lm_glu_clamp_bf16(G.data_ptr(), G.stride(0), U.data_ptr(), U.stride(0), float(limit),
+                                                 float(alpha), float(up_offset), Y.data_ptr(), n, Kp, T, self.s),
+                 "lm_glu_clamp_bf16")
+        return Y
 
     def argmax_rows(self, z, tok, logprob=None):
         B, V = z.shape

@@ -415,10 +415,25 @@ def test_gate_before_the_group_norm_and_plain_gated_unit():
         assert (host(eng, out) - want).abs().max() < 1e-5
         after = O.rms(o.double().view(T, groups, -1), 1e-3).reshape(T, -1) * w.double() * F.silu(z[:, 2:].double())
         assert (want - after).abs().max() > 0.1                      # the order matters
+    # few tokens with long groups: a whole block per group
+    big, zb, wb = torch.randn(2, 1536, generator=g) * 2, torch.randn(2, 1536, generator=g), torch.randn(1536, generator=g).bfloat16()
+    for groups in (1, 3, 6):
+        out = dev(torch.zeros(2, 1536))
+        ops.head_post(dev(big), out, dv=64, gate=dev(zb), gate_silu=True, w=dev(wb, torch.bfloat16), eps=1e-5, span=1536 // groups,
+                      gate_first=True)
+        want = O.rms((big.double() * F.silu(zb.double())).view(2, groups, -1), 1e-5).reshape(2, -1) * wb.double()
+        assert (host(eng, out) - want).abs().max() < 1e-5
     a, b = torch.randn(T, 300, generator=g) * 3, torch.randn(T, 300, generator=g) * 3
     y = dev(torch.zeros(T, 300))
     ops.glu_clamp(dev(a), dev(b), float("inf"), 1.0, y, up_offset=0.0)
     assert (host(eng, y) - F.silu(a.double()) * b.double()).abs().max() < 1e-5
+    wide = dev(torch.cat([a, b], dim=1))                                 # the same as bf16 operand rows, zero-padded
+    yb = ops.glu_clamp_bf16(wide[:, :300], wide[:, 300:], 1.25, 1.702, up_offset=1.0)
+    gg, uu = a.double().clamp(max=1.25), b.double().clamp(-1.25, 1.25)
+    want = (gg * torch.sigmoid(1.702 * gg) * (uu + 1)).float().bfloat16().double()
+    got = host(eng, yb)
+    assert got.shape == (T, 320) and got[:, 300:].abs().max() == 0
+    assert ((got[:, :300] - want).abs() <= 2.0 ** -7 * want.abs() + 1e-6).all()
 
 
 def test_logits_times_a_constant():
