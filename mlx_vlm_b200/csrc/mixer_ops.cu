@@ -373,12 +373,14 @@ __global__ void state_prep_kernel(StatePrepP p) {
   }
 }
 
-template <int P>
+template <int P, bool DELTA>
 __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
   // Tokens are staged CT at a time.  The raw q, k, v, decay and beta inputs of the NEXT group are requested from
   // global memory into registers before the current group is walked, so their latency hides behind the walk.
   // Per token, with S the state before it:  dk = S^T k, dq = S^T q (one pass, one butterfly for both),
   // u = beta (v - decay dk) (or v),  o = decay dq + u (k . q),  S <- decay S + k u^T  — o does not wait for the update.
+  // Without the delta rule (DELTA false) u does not depend on S: the chain from token to token is one multiply-add per
+  // row, the dot product and its butterfly hang off it, and the token loop is unrolled so that they overlap the chain.
   constexpr int CB = LS_THREADS / P, LD = P * LS_RS, DKP = P * LS_R;
   constexpr int CT = P >= 32 ? LS_CT / 2 : LS_CT;       // tokens per group: the staged rows fit static shared memory
   constexpr int NQK = (CT * DKP + LS_THREADS - 1) / LS_THREADS, NV = (CT * CB + LS_THREADS - 1) / LS_THREADS;
@@ -482,6 +484,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     float* op = p.out + (long)(start + c0) * p.ldo + (long)h * p.vdim + col;
     const float* kp = &ks[0][r * LS_RS];
     const float* qp = &qs[0][r * LS_RS];
+#pragma unroll(DELTA ? 1 : 4)
     for (int tk = 0; tk < nc; ++tk, op += p.ldo, kp += LD, qp += LD) {
       const float4 k0 = *reinterpret_cast<const float4*>(kp), k1 = *reinterpret_cast<const float4*>(kp + 4);
       const float4 q0 = *reinterpret_cast<const float4*>(qp), q1 = *reinterpret_cast<const float4*>(qp + 4);
@@ -491,18 +494,18 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;       // two running sums per dot: short dependency chains
 #pragma unroll
       for (int i = 0; i < LS_R; i += 2) {
-        a0 = fmaf(S[i], k_[i], a0); a1 = fmaf(S[i + 1], k_[i + 1], a1);
+        if (DELTA) { a0 = fmaf(S[i], k_[i], a0); a1 = fmaf(S[i + 1], k_[i + 1], a1); }
         b0 = fmaf(S[i], q_[i], b0); b1 = fmaf(S[i + 1], q_[i + 1], b1);
       }
       float dk = a0 + a1, dq = b0 + b1;
 #pragma unroll
       for (int o = 1; o < P; o <<= 1) {
-        dk += __shfl_xor_sync(0xffffffffu, dk, o);
+        if (DELTA) dk += __shfl_xor_sync(0xffffffffu, dk, o);
         dq += __shfl_xor_sync(0xffffffffu, dq, o);
       }
       const float vin = vs[tk][cj];
       float u = vin;
-      if (p.delta) u = bet[tk] * (u - d * dk);
+      if (DELTA) u = bet[tk] * (u - d * dk);
       else if (p.dt_in) u = bet[tk] * u;
       if (r == 0 && valid) *op = fmaf(skip, vin, fmaf(u, kq[tk], d * dq));
 #pragma unroll
@@ -619,6 +622,30 @@ __global__ void glu_clamp_bf16_kernel(const float* __restrict__ G, long ldg, con
       y = g * sigmoid_exact(alpha * g) * (u + up_off);
     }
     Y[t * Kp + i] = f2bf(y);
+  }
+}
+
+// four columns per thread (rows of whole, aligned 16-byte vectors; n and Kp multiples of 4)
+__global__ void glu_clamp_bf16x4_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
+                                        float alpha, float up_off, bf16* __restrict__ Y, int n, int Kp) {
+  const long t = blockIdx.x;
+  for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < Kp; i += blockDim.x * gridDim.y * 4) {
+    float y[4] = {0.f, 0.f, 0.f, 0.f};
+    if (i < n) {
+      const float4 a = *reinterpret_cast<const float4*>(G + t * ldg + i);
+      const float4 b = *reinterpret_cast<const float4*>(U + t * ldu + i);
+      const float gs[4] = {a.x, a.y, a.z, a.w}, us[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float g = fminf(gs[e], lim), u = fminf(fmaxf(us[e], -lim), lim);
+        y[e] = g * sigmoid_exact(alpha * g) * (u + up_off);
+      }
+    }
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const unsigned*>(&lo);
+    pk.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(Y + t * Kp + i) = pk;
   }
 }
 
@@ -771,7 +798,12 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
     p.q = qn; p.ldq = n; p.k = kn; p.ldk = n; p.kq_in = kq; p.dec_in = dec; p.bet_in = bet;
   }
   const dim3 block(LS_THREADS);
-#define LS_LAUNCH(PP) linear_state_kernel<PP><<<dim3(n_seq, H, cdiv(vdim, LS_THREADS / PP)), block, 0, cs>>>(p)
+#define LS_LAUNCH(PP)                                                                                            \
+  do {                                                                                                           \
+    const dim3 grid(n_seq, H, cdiv(vdim, LS_THREADS / PP));                                                      \
+    if (delta) linear_state_kernel<PP, true><<<grid, block, 0, cs>>>(p);                                         \
+    else linear_state_kernel<PP, false><<<grid, block, 0, cs>>>(p);                                              \
+  } while (0)
   if (dim <= LS_R) LS_LAUNCH(1);
   else if (dim <= 2 * LS_R) LS_LAUNCH(2);
   else if (dim <= 4 * LS_R) LS_LAUNCH(4);
@@ -827,7 +859,10 @@ int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float 
 int b200_lm_glu_clamp_bf16(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
                            void* Y, int n, int Kp, int T, void* st) {
   B200_REQUIRE(G && U && Y && T > 0 && n > 0 && Kp >= n, "lm_glu_clamp_bf16: bad argument");
-  glu_clamp_bf16_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp);
+  const bool v4 = n % 4 == 0 && Kp % 4 == 0 && ldg % 4 == 0 && ldu % 4 == 0 && (((uintptr_t)G | (uintptr_t)U) & 15) == 0 &&
+                  ((uintptr_t)Y & 7) == 0;
+  if (v4) glu_clamp_bf16x4_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp);
+  else glu_clamp_bf16_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

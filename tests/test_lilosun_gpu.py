@@ -434,6 +434,8 @@ def test_gate_before_the_group_norm_and_plain_gated_unit():
     got = host(eng, yb)
     assert got.shape == (T, 320) and got[:, 300:].abs().max() == 0
     assert ((got[:, :300] - want).abs() <= 2.0 ** -7 * want.abs() + 1e-6).all()
+    odd = host(eng, ops.glu_clamp_bf16(wide[:, 1:78], wide[:, 301:378], 1.25, 1.702, up_offset=1.0))    # rows that are no vectors
+    assert odd.shape == (T, 128) and torch.equal(odd[:, :77], got[:, 1:78]) and odd[:, 77:].abs().max() == 0
 
 
 def test_logits_times_a_constant():

@@ -106,13 +106,13 @@ def test_scaled_frequencies_of_the_product_and_the_restatement():
     ops = LayerOps.__new__(LayerOps)          # the table needs no device: catch the upload
     ops._inv_freq = {}
     ops.to_device = lambda arr, dtype=None: torch.from_numpy(np.asarray(arr, dtype=np.float64))
-    for base, dims, sc in ((100.0, 4, (4.0, 16, 8.0, 1.0)), (20000.0, 64, (40.0, 4096, 32.0, 1.0)), (10.0, 2, (2.0, 8, 1.0, 1.0)),
+    for base, dims, sc in ((100.0, 4, (4.0, 16, 8.0, 1.0)), (50000.0, 64, (40.0, 4096, 24.0, 2.0)), (10.0, 2, (2.0, 8, 1.0, 1.0)),
                            (500.0, 12, None)):
         want, amp = O.yarn_frequencies(base, dims, None if sc is None else dict(zip(("factor", "original", "fast", "slow"), sc)))
         assert torch.allclose(ops.inv_freq(base, dims, sc), want, rtol=1e-13, atol=0)
         assert abs(LayerOps.rope_amplitude(sc) - amp) < 1e-15
-    f, amp = O.yarn_frequencies(20000.0, 64, {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0})
-    plain, _ = O.yarn_frequencies(20000.0, 64, None)
+    f, amp = O.yarn_frequencies(50000.0, 64, {"factor": 40.0, "original": 4096, "fast": 24.0, "slow": 2.0})
+    plain, _ = O.yarn_frequencies(50000.0, 64, None)
     assert f[0] == plain[0] and abs(f[-1] - plain[-1] / 40.0) < 1e-18 and abs(amp - (0.1 * math.log(40.0) + 1)) < 1e-15
     assert all(plain[i] / 40.0 <= f[i] <= plain[i] for i in range(32))
 
