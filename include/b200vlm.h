@@ -492,9 +492,10 @@ int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, con
 int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
                       float* Y, long ldy, int n, int T, void* stream);
 
-/* the same as bf16 rows of Kp >= n columns (zero-padded): the operand of the next tensor-core product */
+/* the same as bf16 rows of Kp >= n columns (zero-padded): the operand of the next tensor-core product; live != NULL:
+ * rows t with live[t] < 0 (the padding of sorted expert segments) are written as zeros and their inputs are not read */
 int b200_lm_glu_clamp_bf16(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
-                           void* Y, int n, int Kp, int T, void* stream);
+                           void* Y, int n, int Kp, const int* live, int T, void* stream);
 
 #ifdef __cplusplus
 }

@@ -742,6 +742,34 @@ __global__ void rows_to_bf16_kernel(const float* __restrict__ X, long ldx, const
     out[(long)i * ldo + k] = f2bf(v);
   }
 }
+// the same with four columns per thread (rows of whole, aligned 16-byte vectors; K, Kp multiples of 4)
+__global__ void rows_to_bf16x4_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ map, int div,
+                                      bf16* __restrict__ out, long ldo, int K, int Kp, int relu2) {
+  const int i = blockIdx.x;
+  const int src = map ? map[i] : i;
+  const float* x = X + (long)(src < 0 ? 0 : (map ? src / div : src)) * ldx;
+  for (int k = threadIdx.x * 4; k < Kp; k += blockDim.x * 4) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k < K && src >= 0) v = *reinterpret_cast<const float4*>(x + k);
+    if (relu2) {
+      v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
+      v.x *= v.x; v.y *= v.y; v.z *= v.z; v.w *= v.w;
+    }
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const unsigned*>(&lo);
+    pk.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(out + (long)i * ldo + k) = pk;
+  }
+}
+__global__ void rows_scatter4_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ dst_map,
+                                     float* __restrict__ out, long ldo, int K) {
+  const int i = blockIdx.x;
+  if (dst_map[i] < 0) return;                  // a padding row
+  const float4* x = reinterpret_cast<const float4*>(X + (long)i * ldx);
+  float4* o = reinterpret_cast<float4*>(out + (long)dst_map[i] * ldo);
+  for (int k = threadIdx.x; k < K / 4; k += blockDim.x) o[k] = x[k];
+}
 __global__ void rows_scatter_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ dst_map,
                                     float* __restrict__ out, long ldo, int K) {
   const int i = blockIdx.x;
@@ -1124,14 +1152,18 @@ int b200_lm_gemm_rows(const float* X, long ldx, long xb, const void* W, long ldw
 int b200_lm_rows_to_bf16(const float* X, long ldx, const int* map, int div, void* out, long ldo, int T, int K, int Kp,
                          int relu2, void* st) {
   B200_REQUIRE(X && out && T > 0 && K > 0 && Kp >= K, "lm_rows_to_bf16: bad argument");
-  rows_to_bf16_kernel<<<T, 256, 0, (cudaStream_t)st>>>(X, ldx, map, div > 0 ? div : 1, (bf16*)out, ldo, K, Kp, relu2);
+  const bool v4 = K % 4 == 0 && Kp % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)X & 15) == 0 && ((uintptr_t)out & 7) == 0;
+  if (v4) rows_to_bf16x4_kernel<<<T, Kp >= 1024 ? 256 : 128, 0, (cudaStream_t)st>>>(X, ldx, map, div > 0 ? div : 1, (bf16*)out, ldo, K, Kp, relu2);
+  else rows_to_bf16_kernel<<<T, 256, 0, (cudaStream_t)st>>>(X, ldx, map, div > 0 ? div : 1, (bf16*)out, ldo, K, Kp, relu2);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
 
 int b200_lm_rows_scatter(const float* X, long ldx, const int* dst_map, float* out, long ldo, int T, int K, void* st) {
   B200_REQUIRE(X && dst_map && out && T > 0 && K > 0, "lm_rows_scatter: bad argument");
-  rows_scatter_kernel<<<T, 256, 0, (cudaStream_t)st>>>(X, ldx, dst_map, out, ldo, K);
+  const bool v4 = K % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 && (((uintptr_t)X | (uintptr_t)out) & 15) == 0;
+  if (v4) rows_scatter4_kernel<<<T, 256, 0, (cudaStream_t)st>>>(X, ldx, dst_map, out, ldo, K);
+  else rows_scatter_kernel<<<T, 256, 0, (cudaStream_t)st>>>(X, ldx, dst_map, out, ldo, K);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -613,11 +613,13 @@ __global__ void glu_clamp4_kernel(const float* __restrict__ G, long ldg, const f
 
 // the same, written as the bf16 operand rows of the next tensor-core product (zero-padded to Kp columns)
 __global__ void glu_clamp_bf16_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
-                                      float alpha, float up_off, bf16* __restrict__ Y, int n, int Kp) {
+                                      float alpha, float up_off, bf16* __restrict__ Y, int n, int Kp,
+                                      const int* __restrict__ live) {
   const long t = blockIdx.x;
+  const bool pad = live && live[t] < 0;          // a padding row of a sorted segment: zeros, its inputs are not read
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < Kp; i += blockDim.x * gridDim.y) {
     float y = 0.f;
-    if (i < n) {
+    if (i < n && !pad) {
       const float g = fminf(G[t * ldg + i], lim), u = fminf(fmaxf(U[t * ldu + i], -lim), lim);
       y = g * sigmoid_exact(alpha * g) * (u + up_off);
     }
@@ -627,11 +629,13 @@ __global__ void glu_clamp_bf16_kernel(const float* __restrict__ G, long ldg, con
 
 // four columns per thread (rows of whole, aligned 16-byte vectors; n and Kp multiples of 4)
 __global__ void glu_clamp_bf16x4_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
-                                        float alpha, float up_off, bf16* __restrict__ Y, int n, int Kp) {
+                                        float alpha, float up_off, bf16* __restrict__ Y, int n, int Kp,
+                                        const int* __restrict__ live) {
   const long t = blockIdx.x;
+  const bool pad = live && live[t] < 0;
   for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < Kp; i += blockDim.x * gridDim.y * 4) {
     float y[4] = {0.f, 0.f, 0.f, 0.f};
-    if (i < n) {
+    if (i < n && !pad) {
       const float4 a = *reinterpret_cast<const float4*>(G + t * ldg + i);
       const float4 b = *reinterpret_cast<const float4*>(U + t * ldu + i);
       const float gs[4] = {a.x, a.y, a.z, a.w}, us[4] = {b.x, b.y, b.z, b.w};
@@ -857,12 +861,12 @@ int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float 
 }
 
 int b200_lm_glu_clamp_bf16(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
-                           void* Y, int n, int Kp, int T, void* st) {
+                           void* Y, int n, int Kp, const int* live, int T, void* st) {
   B200_REQUIRE(G && U && Y && T > 0 && n > 0 && Kp >= n, "lm_glu_clamp_bf16: bad argument");
   const bool v4 = n % 4 == 0 && Kp % 4 == 0 && ldg % 4 == 0 && ldu % 4 == 0 && (((uintptr_t)G | (uintptr_t)U) & 15) == 0 &&
                   ((uintptr_t)Y & 7) == 0;
-  if (v4) glu_clamp_bf16x4_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp);
-  else glu_clamp_bf16_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp);
+  if (v4) glu_clamp_bf16x4_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp, live);
+  else glu_clamp_bf16_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp, live);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -917,7 +917,7 @@ class GroupedExpertMixture:
         xs = ops.to_bf16(x, self.W, rows=n_rows, row_map=order, div=self.top)
         hs = ops.empty((n_rows, 2 * ff))
         ops.tc_gemm_grouped(xs, w["gu"], hs, group, N_=2 * ff, K=self.W, n_groups=self.E)
-        act = ops.glu_clamp_bf16(hs[:, :ff], hs[:, ff:], self.limit, self.alpha)      # activation and rounding in one pass
+        act = ops.glu_clamp_bf16(hs[:, :ff], hs[:, ff:], self.limit, self.alpha, live=order)   # activation and rounding in one pass
         ys = ops.empty((n_rows, self.W))
         ops.tc_gemm_grouped(act, w["down"], ys, group, N_=self.W, K=ff, n_groups=self.E)
         out = ops.empty((n_all, self.W))

@@ -403,13 +403,14 @@ class LayerOps:
                                             float(alpha), float(up_offset), Y.data_ptr(), Y.stride(0), n, T, self.s),
                  "lm_glu_clamp")
 
-    def glu_clamp_bf16(self, G, U, limit, alpha, up_offset: float = 1.0) -> torch.Tensor:
-        """the gated activation written as bf16 operand rows (T, ceil64(n)) of the next tensor-core product"""
+    def glu_clamp_bf16(self, G, U, limit, alpha, up_offset: float = 1.0, live: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """the gated activation written as bf16 operand rows (T, ceil64(n)) of the next tensor-core product; live (T,)
+        int32: rows with a negative entry (padding of sorted expert segments) become zeros without being read"""
         T, n = G.shape
         Kp = (n + 63) // 64 * 64
         Y = self.empty((T, Kp), torch.bfloat16)
         self._ok(self.lib.b200_lm_glu_clamp_bf16(G.data_ptr(), G.stride(0), U.data_ptr(), U.stride(0), float(limit),
-                                                 float(alpha), float(up_offset), Y.data_ptr(), n, Kp, T, self.s),
+                                                 float(alpha), float(up_offset), Y.data_ptr(), n, Kp, N.ptr(live), T, self.s),
                  "lm_glu_clamp_bf16")
         return Y
 

@@ -434,8 +434,38 @@ def test_gate_before_the_group_norm_and_plain_gated_unit():
     got = host(eng, yb)
     assert got.shape == (T, 320) and got[:, 300:].abs().max() == 0
     assert ((got[:, :300] - want).abs() <= 2.0 ** -7 * want.abs() + 1e-6).all()
+    live = dev(np.asarray([0, -1, 7, -1, 2], np.int32), torch.int32)      # padding rows become zeros, their inputs may hold anything
+    junk = wide.clone()
+    junk[1], junk[3] = float("nan"), float("inf")
+    masked = host(eng, ops.glu_clamp_bf16(junk[:, :300], junk[:, 300:], 1.25, 1.702, up_offset=1.0, live=live))
+    assert torch.equal(masked[[0, 2, 4]], got[[0, 2, 4]]) and masked[[1, 3]].abs().max() == 0
     odd = host(eng, ops.glu_clamp_bf16(wide[:, 1:78], wide[:, 301:378], 1.25, 1.702, up_offset=1.0))    # rows that are no vectors
     assert odd.shape == (T, 128) and torch.equal(odd[:, :77], got[:, 1:78]) and odd[:, 77:].abs().max() == 0
+
+
+@pytest.mark.parametrize("K", [64, 100, 77])
+def test_operand_rows_gathered_and_scattered(K):
+    """fp32 rows -> bf16 operand rows through a row map with padding entries, and product rows back to entry order"""
+    eng = _eng()
+    ops = eng.ops
+    g = torch.Generator().manual_seed(K)
+    x = torch.randn(9, K + 4, generator=g)
+    order = np.asarray([5, -1, 0, 17, 16, -1, -1, 3], np.int32)           # entry e reads row e // 2
+    xb = host(eng, ops.to_bf16(dev(x)[:, 4:], K, rows=8, row_map=dev(order, torch.int32), div=2))
+    Kp = (K + 63) // 64 * 64
+    assert xb.shape == (8, Kp)
+    for i, e in enumerate(order):
+        want = torch.zeros(Kp, dtype=torch.float64) if e < 0 else F.pad(x[e // 2, 4:].bfloat16().double(), (0, Kp - K))
+        assert torch.equal(xb[i], want)
+    y = torch.randn(8, K, generator=g)
+    out = dev(torch.full((18, K + 4), -5.0))
+    ops.rows_scatter(dev(y), dev(order, torch.int32), out[:, 4:], 8)
+    got = host(eng, out)[:, 4:]
+    for i, e in enumerate(order):
+        if e >= 0:
+            assert torch.equal(got[e], y[i].double())
+    untouched = [r for r in range(18) if r not in set(order.tolist())]
+    assert (got[untouched] == -5.0).all()
 
 
 def test_logits_times_a_constant():
