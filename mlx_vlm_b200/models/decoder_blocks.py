@@ -882,7 +882,7 @@ class GroupedExpertMixture:
 
     def forward(self, ctx: StepCtx, x: torch.Tensor) -> dict:
         ops, w, T, ff = ctx.ops, self.w, x.shape[0], self.ff
-        z = ops.linear(x, w["router"])
+        z = ops.linear(x, w["router"], exact_x=True)      # scores decide the choice: fp32 input rows in every mode
         idx, wgt = ops.router_group_topk(z, self.top, w["correction"], self.n_groups, self.keep, E=self.E)
         lists, count = ops.moe_group(idx, self.E)
         out = None

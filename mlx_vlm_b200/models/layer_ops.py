@@ -198,14 +198,15 @@ class LayerOps:
         return lists, count
 
     def gemm(self, X, W, Y, *, M, N_, K, ldx=None, xb=0, ldw=None, wb=0, ldy=None, yb=0, batch=1, bias=None,
-             lists=None, count=None, x_div=1, epi=EPI_NONE, epi_param=0.0, compact=0):
+             lists=None, count=None, x_div=1, epi=EPI_NONE, epi_param=0.0, compact=0, exact_x: bool = False):
         """Y[b][r][:] = epi(X[b][r'] . W[b]^T + bias); strides in elements (default: the tensors' own rows).
-        compact: an upper bound of the batches that have rows (a decode step: rows x top experts of many)"""
+        compact: an upper bound of the batches that have rows (a decode step: rows x top experts of many);
+        exact_x: the rows of X are not rounded to bf16 in the serving mode either (a router's input)"""
         self._ok(self.lib.b200_lm_gemm_rows(
             X.data_ptr(), X.stride(0) if ldx is None else ldx, xb, W.data_ptr(), K if ldw is None else ldw, wb,
             N.ptr(bias), Y.data_ptr(), Y.stride(0) if ldy is None else ldy, yb, N.ptr(lists),
             lists.stride(0) if lists is not None else 0, N.ptr(count), x_div, M, N_, K, batch, epi, float(epi_param),
-            int(not self.exact), int(M <= SKINNY_ROWS), int(compact), self.s), "lm_gemm_rows")
+            int(not self.exact and not exact_x), int(M <= SKINNY_ROWS), int(compact), self.s), "lm_gemm_rows")
 
     # ---- the tensor-core path of prompt steps (bf16 serving mode) ----------------------------------------
     def tc_ok(self, rows: int, *ks: int) -> bool:
@@ -288,21 +289,24 @@ class LayerOps:
         return out
 
     def linear(self, X: torch.Tensor, W: torch.Tensor, bias=None, epi=EPI_NONE, epi_param=0.0,
-               out: Optional[torch.Tensor] = None, add: bool = False) -> torch.Tensor:
+               out: Optional[torch.Tensor] = None, add: bool = False, exact_x: bool = False) -> torch.Tensor:
         """Y = epi(X . W^T + bias).  X and W may be column ranges of wider rows (their row pitch is taken from the
-        tensors).  out: the rows to write (else fresh ones); add: the product is added to what `out` holds."""
+        tensors).  out: the rows to write (else fresh ones); add: the product is added to what `out` holds;
+        exact_x: fp32 rows of X against the weights on the row kernels in every mode (small products whose result
+        decides something: a router)."""
         (T, K), n = X.shape, W.shape[0]
         Y = self.empty((T, n)) if out is None else out
         ldw = W.stride(0) if n > 1 else K
         if add:
             assert out is not None and epi == EPI_NONE, "linear: adding needs the rows to add to and no other epilogue"
-        if epi == EPI_NONE and self.tc_ok(T, K, ldw) and W.data_ptr() % 16 == 0:
+        if epi == EPI_NONE and not exact_x and self.tc_ok(T, K, ldw) and W.data_ptr() % 16 == 0:
             try:
                 self.tc_gemm(self.to_bf16(X, K), W, Y, N_=n, K=K, ldw=ldw, bias=bias, res=Y if add else None)
                 return Y
             except N.B200Error as e:
                 self.tc_refused(e)
-        self.gemm(X, W, Y, M=T, N_=n, K=K, ldw=ldw, bias=bias, epi=EPI_ADD if add else epi, epi_param=epi_param)
+        self.gemm(X, W, Y, M=T, N_=n, K=K, ldw=ldw, bias=bias, epi=EPI_ADD if add else epi, epi_param=epi_param,
+                  exact_x=exact_x)
         return Y
 
     # ---- sequences of a step, and the mixers that carry a state along them (csrc/mixer_ops.cu) -------------------
