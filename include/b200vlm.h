@@ -384,6 +384,11 @@ int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T,
  * taken off first (a layer norm without bias). */
 int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const void* w, float w_offset, float eps,
                       float* x, long ldx, int add, const int* rows, int center, int T, int N, void* stream);
+/* the residual update of b200_lm_residual_rows on res (stored back) followed by the norm of the updated row into out:
+ * res[t] += ls * (...); out[t] = norm(res[t]) * (w_offset + w) */
+int b200_lm_residual_norm_rows(const float* y, long ldy, const float* wgt, int top, const float* shared, long lds,
+                               const float* sgate, long ldsg, const void* ls, float* res, long ldr, const void* w,
+                               float w_offset, float eps, int center, float* out, long ldo, int T, int N, void* stream);
 /* D[t] = [q latent | kv latent | rotated key part] (the fused down-projection): cq = rmsnorm(q latent) * wq;
  * own_kv: rmsnorm(kv latent) * wkv and the rotated part go to cache[slot[t]][pos[t]] = [kv_rank | rot_dim] */
 int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wkv, float eps, float* cq, long ldq,

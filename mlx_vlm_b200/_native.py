@@ -120,6 +120,7 @@ LM_SIGNATURES = {
     "b200_lm_router_topk": (_I, [_P, _L, _I, _I, _P, _P, _I, _P]),
     "b200_lm_router_group_topk": (_I, [_P, _L, _P, _I, _I, _I, _I, _P, _P, _I, _P]),
     "b200_lm_residual_rows": (_I, [_P, _L, _P, _I, _P, _L, _P, _L, _P, _P, _L, _I, _I, _P]),
+    "b200_lm_residual_norm_rows": (_I, [_P, _L, _P, _I, _P, _L, _P, _L, _P, _P, _L, _P, _F, _F, _I, _P, _L, _I, _I, _P]),
     "b200_lm_moe_group": (_I, [_P, _I, _I, _P, _L, _P, _P]),
     "b200_lm_gemm_rows": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                                _I, _I, _P]),
@@ -133,6 +134,7 @@ LM_SIGNATURES = {
     "b200_lm_masked_softmax_bf16": (_I, [_P, _L, _P, _I, _F, _P, _L, _I, _I, _P]),
     "b200_lm_cache_transpose": (_I, [_P, _L, _I, _I, _I, _P, _P]),
     "b200_gemm_wt_f32": (_I, [_P, _L, _P, _L, _P, _P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _P]),
+    "b200_f32_split": (_I, [_P, _L, _P, _L, _I, _I, _I, _P]),
     "b200_lm_advance_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _P]),
     # csrc/mixer_ops.cu
     "b200_lm_short_conv": (_I, [_P, _L, _P, _P, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P]),

@@ -73,6 +73,12 @@ struct NormP {
   const int* rows;                    // input row of output t (NULL: t)
   int N;
   int center;
+  // a residual update in front of the norm (res != NULL; no `rows`): the normed row is
+  // res[t] <- res[t] + ls * (y row (or the combined rows) + sigmoid(sgate[t]) shared[t]), stored back, then normed into x
+  float* res; long ldr;
+  const bf16* ls;
+  const float* shared; long lds;
+  const float* sgate; long ldsg;
 };
 __global__ void norm_rows_kernel(NormP p) {
   extern __shared__ float sm[];
@@ -80,6 +86,7 @@ __global__ void norm_rows_kernel(NormP p) {
   float* red = sm + p.N;              // 32
   const int t = blockIdx.x;
   const long r = p.rows ? p.rows[t] : t;
+  const float sg = (p.res && p.shared) ? (p.sgate ? 1.0f / (1.0f + expf(-p.sgate[r * p.ldsg])) : 1.f) : 0.f;
   float ss = 0.f;
   for (int i = threadIdx.x; i < p.N; i += blockDim.x) {
     float v;
@@ -88,6 +95,12 @@ __global__ void norm_rows_kernel(NormP p) {
       for (int s = 0; s < p.top; ++s) v += p.wgt[r * p.top + s] * p.y[(r * p.top + s) * p.ldy + i];
     } else {
       v = p.y[r * p.ldy + i];
+    }
+    if (p.res) {                      // the same arithmetic, in the same order, as residual_rows_kernel
+      if (p.shared) v = fmaf(sg, p.shared[r * p.lds + i], v);
+      float* o = p.res + r * p.ldr + i;
+      v = fmaf(p.ls ? bf2f(p.ls[i]) : 1.f, v, *o);
+      *o = v;
     }
     row[i] = v;
     ss += p.center ? v : v * v;
@@ -1005,7 +1018,19 @@ int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const
                       float* x, long ldx, int add, const int* rows, int center, int T, int N, void* st) {
   B200_REQUIRE(y && w && x && T > 0 && N > 0, "lm_norm_rows: bad argument");
   B200_REQUIRE((N + 32) * 4 <= 48 * 1024, "lm_norm_rows: rows of %d numbers do not fit shared memory", N);
-  NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, x, ldx, add, rows, N, center};
+  NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, x, ldx, add, rows, N, center, nullptr, 0, nullptr, nullptr, 0, nullptr, 0};
+  norm_rows_kernel<<<T, T < 64 ? 1024 : 256, (N + 32) * sizeof(float), (cudaStream_t)st>>>(p);
+  B200_CHECK_LAUNCH();
+  return B200_OK;
+}
+
+int b200_lm_residual_norm_rows(const float* y, long ldy, const float* wgt, int top, const float* shared, long lds,
+                               const float* sgate, long ldsg, const void* ls, float* res, long ldr, const void* w,
+                               float w_offset, float eps, int center, float* out, long ldo, int T, int N, void* st) {
+  B200_REQUIRE(y && res && w && out && T > 0 && N > 0 && (top == 0 || wgt), "lm_residual_norm_rows: bad argument");
+  B200_REQUIRE((N + 32) * 4 <= 48 * 1024, "lm_residual_norm_rows: rows of %d numbers do not fit shared memory", N);
+  NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, out, ldo, 0, nullptr, N, center,
+          res, ldr, (const bf16*)ls, shared, lds, sgate, ldsg};
   norm_rows_kernel<<<T, T < 64 ? 1024 : 256, (N + 32) * sizeof(float), (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
   return B200_OK;

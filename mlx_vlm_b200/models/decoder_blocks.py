@@ -974,14 +974,29 @@ class ScaledPreNormLayer:
         if self.ff is not None:
             self.ff.bind(p + "mlp.", view)
 
-    def forward(self, ctx: StepCtx, x: torch.Tensor):
+    def forward(self, ctx: StepCtx, x: torch.Tensor, normed: Optional[torch.Tensor] = None,
+                next_norm: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """normed: LN1(x) if the layer before already made it; next_norm: the weight of the norm that follows this layer
+        — then the layer's last residual update also norms the updated rows, and the result is returned"""
         ops = ctx.ops
-        n = ops.empty(tuple(x.shape))
-        ops.norm_rows(x, self.w["norm1"], ctx.eps, n, center=True)
-        ops.residual_rows(self.mixer.forward(ctx, n), x, self.w["ls1"])
-        if self.ff is not None:
-            ops.norm_rows(x, self.w["norm2"], ctx.eps, n, center=True)
-            ops.residual_rows(x=x, ls=self.w["ls2"], **self.ff.forward(ctx, n))
+        n = normed
+        if n is None:
+            n = ops.empty(tuple(x.shape))
+            ops.norm_rows(x, self.w["norm1"], ctx.eps, n, center=True)
+        y = self.mixer.forward(ctx, n)
+        if self.ff is None:
+            return self._close(ctx, x, self.w["ls1"], {"y": y}, next_norm)
+        n2 = self._close(ctx, x, self.w["ls1"], {"y": y}, self.w["norm2"])
+        return self._close(ctx, x, self.w["ls2"], self.ff.forward(ctx, n2), next_norm)
+
+    def _close(self, ctx: StepCtx, x, ls, branch: dict, norm_w):
+        """x += ls * branch; with a norm weight: also the norm of the updated rows (one launch), returned"""
+        if norm_w is None:
+            ctx.ops.residual_rows(x=x, ls=ls, **branch)
+            return None
+        n = ctx.ops.empty(tuple(x.shape))
+        ctx.ops.residual_norm_rows(x=x, ls=ls, w=norm_w, eps=ctx.eps, out=n, center=True, **branch)
+        return n
 
 
 def assign_cache_layers(layers: List[PostNormLayer]) -> int:

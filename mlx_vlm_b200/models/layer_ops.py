@@ -139,6 +139,19 @@ class LayerOps:
                                                 shared_gate.stride(0) if shared_gate is not None else 0, N.ptr(ls),
                                                 x.data_ptr(), x.stride(0), T, n, self.s), "lm_residual_rows")
 
+    def residual_norm_rows(self, y: torch.Tensor, x: torch.Tensor, ls: Optional[torch.Tensor], w: torch.Tensor, eps: float,
+                           out: torch.Tensor, *, center: bool = False, w_offset: float = 0.0,
+                           combine: Optional[torch.Tensor] = None, top: int = 0, shared: Optional[torch.Tensor] = None,
+                           shared_gate: Optional[torch.Tensor] = None):
+        """the update of `residual_rows` on x and, in the same launch, out = norm(updated x) * (w_offset + w): the
+        branch's end and the next sublayer's norm read and write the row once"""
+        T, n = x.shape
+        self._ok(self.lib.b200_lm_residual_norm_rows(
+            y.data_ptr(), y.stride(0), N.ptr(combine), int(top), N.ptr(shared), shared.stride(0) if shared is not None else 0,
+            N.ptr(shared_gate), shared_gate.stride(0) if shared_gate is not None else 0, N.ptr(ls), x.data_ptr(), x.stride(0),
+            w.data_ptr(), float(w_offset), float(eps), int(center), out.data_ptr(), out.stride(0), T, n, self.s),
+            "lm_residual_norm_rows")
+
     def latent_post(self, D, wq, wkv, eps, cq, cache_layer, slot, pos, cs, q_rank, kv_rank, rot_dim, rot_dims,
                     pairs: bool = False):
         """cache_layer: (slots, capacity, kv_rank + rot_dim) view of the pool, or None for a layer that borrows;
@@ -233,14 +246,25 @@ class LayerOps:
         return out
 
     def tc_gemm(self, Xb: torch.Tensor, W: torch.Tensor, Y: torch.Tensor, *, N_: int, K: int, ldw: Optional[int] = None,
-                ldy: Optional[int] = None, bias=None, rows: Optional[int] = None, res: Optional[torch.Tensor] = None):
+                ldy: Optional[int] = None, bias=None, rows: Optional[int] = None, res: Optional[torch.Tensor] = None,
+                parts: int = 1):
         """Y[rows, N_] (fp32) = Xb[rows, ceil64(K)] (bf16) . W[N_, K]^T (bf16, row pitch ldw) (+ res, which may be Y
-        itself: a stream that accumulates in place) on tcgen05"""
+        itself: a stream that accumulates in place) on tcgen05.  parts = 2: Xb holds [hi | lo] halves of fp32 rows
+        (`to_split`), both multiplied by W and summed in the accumulator"""
         rows = Xb.shape[0] if rows is None else rows
         self._ok(self.lib.b200_gemm_wt_f32(Xb.data_ptr(), Xb.stride(0), W.data_ptr(), K if ldw is None else ldw,
                                            N.ptr(bias), N.ptr(res), res.stride(0) if res is not None else 0,
                                            Y.data_ptr(), Y.stride(0) if ldy is None else ldy, 0, 0, 0,
-                                           rows, N_, K, 1, 0, WT_F32, self.s), "gemm_wt_f32")
+                                           rows, N_, K, int(parts), 0, WT_F32, self.s), "gemm_wt_f32")
+
+    def to_split(self, X: torch.Tensor, K: int) -> torch.Tensor:
+        """fp32 rows -> (T, 2 ceil64(K)) bf16 = [hi | lo] with hi = bf16(x), lo = bf16(x - hi): sixteen more mantissa
+        bits of x reach the tensor cores than with one rounded part (K a multiple of 4)"""
+        T, Kp = X.shape[0], (K + 63) // 64 * 64
+        with torch.cuda.stream(self.stream):
+            out = torch.zeros((T, 2 * Kp), dtype=torch.bfloat16, device=self.device)
+        self._ok(self.lib.b200_f32_split(X.data_ptr(), X.stride(0), out.data_ptr(), 2 * Kp, Kp, T, K, self.s), "f32_split")
+        return out
 
     def moe_order(self, lists: torch.Tensor, count: torch.Tensor) -> torch.Tensor:
         E, T = lists.shape
@@ -292,16 +316,21 @@ class LayerOps:
                out: Optional[torch.Tensor] = None, add: bool = False, exact_x: bool = False) -> torch.Tensor:
         """Y = epi(X . W^T + bias).  X and W may be column ranges of wider rows (their row pitch is taken from the
         tensors).  out: the rows to write (else fresh ones); add: the product is added to what `out` holds;
-        exact_x: fp32 rows of X against the weights on the row kernels in every mode (small products whose result
-        decides something: a router)."""
+        exact_x: the rows of X are not rounded to one bf16 part in the serving mode (small products whose result
+        decides something: a router): fp32 rows on the row kernels, or, for a long step, [hi | lo] halves on the
+        tensor cores."""
         (T, K), n = X.shape, W.shape[0]
         Y = self.empty((T, n)) if out is None else out
         ldw = W.stride(0) if n > 1 else K
         if add:
             assert out is not None and epi == EPI_NONE, "linear: adding needs the rows to add to and no other epilogue"
-        if epi == EPI_NONE and not exact_x and self.tc_ok(T, K, ldw) and W.data_ptr() % 16 == 0:
+        if epi == EPI_NONE and self.tc_ok(T, K, ldw) and W.data_ptr() % 16 == 0 and \
+                (not exact_x or (X.stride(0) % 4 == 0 and X.data_ptr() % 16 == 0)):
             try:
-                self.tc_gemm(self.to_bf16(X, K), W, Y, N_=n, K=K, ldw=ldw, bias=bias, res=Y if add else None)
+                if exact_x:
+                    self.tc_gemm(self.to_split(X, K), W, Y, N_=n, K=K, ldw=ldw, bias=bias, res=Y if add else None, parts=2)
+                else:
+                    self.tc_gemm(self.to_bf16(X, K), W, Y, N_=n, K=K, ldw=ldw, bias=bias, res=Y if add else None)
                 return Y
             except N.B200Error as e:
                 self.tc_refused(e)

@@ -57,6 +57,15 @@ class Model:
     def engine(self) -> LayerEngine:
         return self._engine()
 
+    def run_layers(self, ctx, x: torch.Tensor, embed_again) -> torch.Tensor:
+        """the layers of one step over the residual rows x (T, width) fp32, updated in place.  The last residual update
+        of a layer also norms the rows for the layer that follows (one launch for both)."""
+        n = None
+        for i, L in enumerate(self.layers):
+            nxt = self.layers[i + 1].w["norm1"] if i + 1 < len(self.layers) else None
+            n = L.forward(ctx, x, normed=n, next_norm=nxt)
+        return x
+
     # ------------------------------------------------------------------ weights
     def _globals(self):
         return [("embed", (self.vocab, self.width)), ("final.norm", (self.width,)), ("head", (self.vocab, self.width))]

@@ -174,6 +174,20 @@ def test_layer_norm_and_scaled_residual():
     want = x0.double() + ls.double() * ((ye.double().view(T, top, N) * wg.double()[:, :, None]).sum(1)
                                         + torch.sigmoid(sg[:, 8:].double()) * sh[:, 5:].double())
     assert (host(eng, x) - want).abs().max() < 1e-5
+    # the same update and the norm of the updated rows in one launch; few rows and many (two block sizes)
+    for rows in (T, 70):
+        xr, yr = torch.randn(rows, N, generator=g) + 2.0, torch.randn(rows * top, N, generator=g)
+        wr, shr, sgr = torch.rand(rows, top, generator=g), torch.randn(rows, N, generator=g), torch.randn(rows, 1, generator=g)
+        x, n = dev(xr), dev(torch.zeros(rows, N))
+        ops.residual_norm_rows(dev(yr), x, dev(ls, torch.bfloat16), dev(w, torch.bfloat16), 1e-3, n, center=True, combine=dev(wr),
+                               top=top, shared=dev(shr), shared_gate=dev(sgr))
+        want = xr.double() + ls.double() * ((yr.double().view(rows, top, N) * wr.double()[:, :, None]).sum(1)
+                                            + torch.sigmoid(sgr.double()) * shr.double())
+        assert (host(eng, x) - want).abs().max() < 1e-5
+        assert (host(eng, n) - O.layer_norm(want, w.double(), 1e-3)).abs().max() < 2e-5
+        x, n = dev(xr), dev(torch.zeros(rows, N))
+        ops.residual_norm_rows(dev(shr), x, None, dev(w, torch.bfloat16), 1e-3, n, center=True)
+        assert (host(eng, n) - O.layer_norm(xr.double() + shr.double(), w.double(), 1e-3)).abs().max() < 2e-5
 
 
 @pytest.mark.parametrize("scaling", [None, (4.0, 32, 16.0, 2.0), (16.0, 4096, 32.0, 1.0), (2.0, 8, 1.0, 1.0)])
@@ -478,6 +492,24 @@ def test_logits_times_a_constant():
         assert (host(eng, z) - 0.37 * (x.double() @ W.double().T)).abs().max() < 1e-5
 
 
+@pytest.mark.parametrize("M", [3, 40, 130, 300])
+def test_router_product_keeps_its_input_unrounded_in_the_serving_mode(M):
+    """few rows: fp32 rows on the row kernels; a long step: [hi | lo] halves on the tensor cores (2^-17 of the input)"""
+    eng = _eng(exact=False)
+    g = torch.Generator().manual_seed(M)
+    K, N_ = 72, 9
+    x = torch.randn(M, K + 4, generator=g) * 3
+    W = (torch.randn(N_, K, generator=g) / 8).bfloat16()
+    xd = dev(x)
+    want = x[:, 4:].double() @ W.double().T
+    with eng.ops.on_stream():
+        z = eng.ops.linear(xd[:, 4:], dev(W, torch.bfloat16), exact_x=True)
+        rounded = eng.ops.linear(xd[:, 4:], dev(W, torch.bfloat16))
+    assert (host(eng, z) - want).abs().max() < 2e-4
+    assert (host(eng, rounded) - want).abs().max() > 2e-3          # one rounded part is two orders further off
+    assert eng.ops.tc_enabled
+
+
 # ------------------------------------------------------------------------------------------------ the model
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_whole_prompt_and_every_layer(dtype):
@@ -493,9 +525,10 @@ def test_whole_prompt_and_every_layer(dtype):
         real = [L.forward for L in model.layers]
         try:
             for L, f in zip(model.layers, real):
-                def wrapped(c, xx, f=f):
-                    f(c, xx)
+                def wrapped(c, xx, f=f, **kw):
+                    out = f(c, xx, **kw)
                     seen.append(host(eng, xx))
+                    return out
                 L.forward = wrapped
             lm.step([toks], [lm.make_cache()])
         finally:
