@@ -381,14 +381,16 @@ int b200_lm_embed(const int* tokens, const void* embed, float scale, float* x, i
 int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T, int half, float amp, void* stream);
 /* n = y / sqrt(mean(y^2) + eps) * (w_offset + w); x = n or (add) x += n.  wgt != NULL: y row t is the weighted
  * sum of rows t*top .. t*top+top-1 of y.  rows != NULL: the input row of output t is rows[t].  center: y's mean is
- * taken off first (a layer norm without bias). */
+ * taken off first (a layer norm without bias).
+ * groups > 1: the row is `groups` equal consecutive parts, each with its own root mean square (no centering) */
 int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const void* w, float w_offset, float eps,
-                      float* x, long ldx, int add, const int* rows, int center, int T, int N, void* stream);
+                      float* x, long ldx, int add, const int* rows, int center, int groups, int T, int N, void* stream);
 /* the residual update of b200_lm_residual_rows on res (stored back) followed by the norm of the updated row into out:
- * res[t] += ls * (...); out[t] = norm(res[t]) * (w_offset + w) */
+ * res[t] += ls * mult * (...); out[t] = norm(res[t]) * (w_offset + w), the norm in `groups` parts */
 int b200_lm_residual_norm_rows(const float* y, long ldy, const float* wgt, int top, const float* shared, long lds,
                                const float* sgate, long ldsg, const void* ls, float* res, long ldr, const void* w,
-                               float w_offset, float eps, int center, float* out, long ldo, int T, int N, void* stream);
+                               float w_offset, float eps, int center, float* out, long ldo, int groups, float mult,
+                               int T, int N, void* stream);
 /* D[t] = [q latent | kv latent | rotated key part] (the fused down-projection): cq = rmsnorm(q latent) * wq;
  * own_kv: rmsnorm(kv latent) * wkv and the rotated part go to cache[slot[t]][pos[t]] = [kv_rank | rot_dim] */
 int b200_lm_latent_post(const float* D, long ldd, const void* wq, const void* wkv, float eps, float* cq, long ldq,
@@ -409,12 +411,14 @@ int b200_lm_latent_attention(const float* qa, long ldqa, const void* cache, int 
 /* the `top` largest of z[t][0..E) (lowest index wins a tie) and the softmax over them */
 int b200_lm_router_topk(const float* z, long ldz, int E, int top, int* idx, float* wgt, int T, void* stream);
 /* s = sigmoid(z); the `top` largest of s + correction among the experts of the `keep` best of n_groups equal groups
- * of neighbours (a group's score: the sum of its two largest s + correction); weights = chosen s / (their sum + 1e-20) */
+ * of neighbours (a group's score: the sum of its two largest s + correction); weights = chosen s / (their sum + 1e-20).
+ * softmax: s = softmax(z) over all experts; group_max: a group's score is its largest s + correction */
 int b200_lm_router_group_topk(const float* z, long ldz, const void* correction, int E, int top, int n_groups, int keep,
-                              int* idx, float* wgt, int T, void* stream);
-/* x[t] += ls * (sum_s wgt[t][s] y[t top + s] (top = 0: y[t]) + sigmoid(sgate[t]) shared[t] (if shared)); ls: bf16 [N] or NULL */
+                              int softmax, int group_max, int* idx, float* wgt, int T, void* stream);
+/* x[t] += ls * mult * (sum_s wgt[t][s] y[t top + s] (top = 0: y[t]) + sigmoid(sgate[t]) shared[t] (if shared)); ls: bf16 [N] or NULL */
 int b200_lm_residual_rows(const float* y, long ldy, const float* wgt, int top, const float* shared, long lds,
-                          const float* sgate, long ldsg, const void* ls, float* x, long ldx, int T, int N, void* stream);
+                          const float* sgate, long ldsg, const void* ls, float mult, float* x, long ldx, int T, int N,
+                          void* stream);
 /* list[e][0..count[e]) = the entries i (ascending) with idx[i] == e */
 int b200_lm_moe_group(const int* idx, int n_entries, int E, int* list, long list_stride, int* count, void* stream);
 /* Y[b][r][n] = epi(sum_k X[b][xr][k] W[b][n][k] + bias[n]); list/count: rows of batch b are the entries
@@ -455,51 +459,67 @@ int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* acti
 /* tokens one after the other: first[t] = row of the first token of t's        */
 /* sequence, seqs[g] = (first row, rows).  State buffers are fp32 per slot.    */
 /* ------------------------------------------------------------------------- */
-/* Y[t][c] = act(bias[c] + sum_j w[c][j] U[t - (taps-1) + j][c]) (bias may be NULL); inputs before the step come from state[slot] = the
+/* Y[t][c] = act(bias[c] + [U[t][c] if residual] + sum_j w[c][j] U[t - (taps-1) + j][c]) (bias may be NULL); inputs before the step come from state[slot] = the
  * taps-1 inputs before the step's first token ([taps-1][C]), zeros before position 0; the state is then advanced */
 int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
                        const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
-                       int act, const void* bias, int T, void* stream);
-/* rotate-half rotary (first rot_dims of every head) on Q in place and on K; cache[slot[t]][pos[t]] = [K | V] */
+                       int act, const void* bias, int residual, int T, void* stream);
+/* token shift: M[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s] (mu: bf16 [n_mix][C]); the row before a sequence's first token
+ * of the step is state[slot] ([C]; zeros at position 0), which then keeps the sequence's last row.  single: every
+ * sequence of the step brings one token (the update happens in the same launch) */
+int b200_lm_token_shift(const float* h, long ldh, const void* mu, float* M, long ldm, long mix_stride, float* state,
+                        long slot_stride, const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C,
+                        int n_mix, int single, int T, void* stream);
+/* rotate-half rotary (first rot_dims of every head) on Q in place and on K; cache[slot[t]][pos[t]] = [K | V].
+ * Optional steps before that: qn_w / kn_w (bf16 [H dim] / [G dim]): RMS norm (eps) over the whole query / key projection
+ * times the weight; qt_every > 0: Q times 1 + qt_coef ln(floor((pos + 1) / qt_every) + 1); v_unit: every value head
+ * divided by its root mean square; vmix (one bf16 number lam): V <- (1 - lam) V + lam v_first[t]; v_keep: the values
+ * as cached, in fp32 */
 int b200_lm_qkv_post(float* Q, long ldq, const float* K, long ldk, const float* V, long ldv, void* cache, int cache_bf16,
                      long slot_stride, long tok_stride, const int* slot, const int* pos, const float* cs, int H, int G,
-                     int dim, int vdim, int rot_dims, int T, void* stream);
+                     int dim, int vdim, int rot_dims, const void* qn_w, const void* kn_w, float eps, int v_unit, float qt_coef,
+                     int qt_every, const void* vmix, const float* v_first, long ldvf, float* v_keep, long ldvk, int T,
+                     void* stream);
 /* out[t][h] = softmax over the visible rows j of slot[t] (and the sink logit of head h, if any) of
  * scale * q[t][h] . K_j[h / (H/G)], times V_j; visible: max(block start of pos[t] (chunk > 0), pos[t] - window + 1
- * (window > 0), 0) <= j <= pos[t].  n_split > 1: key tiles dealt to n_split blocks, part [T][H][n_split][vdim + 2] */
+ * (window > 0), 0) <= j <= pos[t].  bias_exp > 0: 2^(-bias_exp (h + 1) / H) (pos[t] - j) is taken off the score;
+ * unit_sink: the denominator also holds 1 (a sink logit of zero).  n_split > 1: key tiles dealt to n_split blocks, part [T][H][n_split][vdim + 2] */
 int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cache_bf16, long slot_stride, long tok_stride,
                            const int* slot, const int* pos, float* out, long ldo, const void* sink, int H, int G,
-                           int dim, int vdim, float scale, int chunk, int window, float* part, int n_split, int T,
-                           void* stream);
+                           int dim, int vdim, float scale, int chunk, int window, float bias_exp, int unit_sink, float* part,
+                           int n_split, int T, void* stream);
 /* per head a (dim, vdim) state carried through each sequence: S <- decay S + k u^T, out = S^T q, u = v or
  * (delta) beta (v - (decay S)^T k); decay per head (decay_const) or exp(-exp(A_log) softplus(a + dt_bias)) per
  * token; beta = sigmoid(b) or 1; q, k shared by `rep` heads, optionally silu'd (act) and scaled to unit length.
  * dt_in (state-space form): u = softplus(a + dt_bias) v; skip != NULL ([H], bf16): out += skip[h] v.
  * prep != NULL (a prompt step; T tokens): scratch of T * (2 (H / rep) dim + H / rep + 2 H) floats — the per-token work
- * (activation, unit lengths, k . q, decay, beta) runs first as one parallel pass and the walk reads its results */
+ * (activation, unit lengths, k . q, decay, beta) runs first as one parallel pass and the walk reads its results.
+ * wraw != NULL ([T][H dim]; needs prep of T * (3 H dim + H) floats, rep 1): a decay per key channel w = exp(-exp(wraw))
+ * and a bonus (bf16 [H][dim]) for the current token: out = S^T q + (sum_i q_i bonus_i k_i) v, then S <- diag(w) S + k v^T */
 int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv, float* out, long ldo,
                          float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
                          int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
                          const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
-                         const float* b, long ldb, int delta, int dt_in, const void* skip, float* prep, int T,
-                         void* stream);
+                         const float* b, long ldb, int delta, int dt_in, const void* skip, const float* wraw, long ldwr,
+                         const void* bonus, float* prep, int T, void* stream);
 /* operands of the tensor-core attention of a prompt step: out[(t, r)] = bf16 of q[t][r * dim .. + dim) padded to Kp;
  * P[(t, r)][j] = softmax over the visible keys key0 + j (and sink[r]) of scale * S[(t, r)][j], bf16, zero elsewhere */
 int b200_lm_heads_to_bf16(const float* q, long ldq, int rep, int dim, void* out, int Kp, int T, void* stream);
 int b200_lm_sink_softmax_bf16(const float* S, long lds, const int* pos, int rep, const void* sink, float scale, int chunk,
-                              int window, int key0, void* P, long ldp, int rows, int Sp, void* stream);
+                              int window, int key0, float bias_exp, int head0, int H, int unit_sink, void* P, long ldp,
+                              int rows, int Sp, void* stream);
 /* out[t][c] = scale * o[t][c] * [rsqrt(mean over c's group of `span` + eps)] * [w[c mod w_len]] * [act(gate)];
  * gate_first: the gate is applied before the norm (the mean square is that of the gated numbers) */
 int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, const void* w, int w_len, float eps, int span,
                       int gate_per_head, int gate_silu, int dv, int n, float scale, float* out, long ldo, int gate_first,
                       int T, void* stream);
-/* Y = g sigmoid(alpha g) (u + up_off), g = min(G, limit), u = clamp(U, -limit, limit) */
-int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
+/* Y = g sigmoid(alpha (g + cubic g^3)) (u + up_off), g = min(G, limit), u = clamp(U, -limit, limit) */
+int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float cubic, float up_off,
                       float* Y, long ldy, int n, int T, void* stream);
 
 /* the same as bf16 rows of Kp >= n columns (zero-padded): the operand of the next tensor-core product; live != NULL:
  * rows t with live[t] < 0 (the padding of sorted expert segments) are written as zeros and their inputs are not read */
-int b200_lm_glu_clamp_bf16(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
+int b200_lm_glu_clamp_bf16(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float cubic, float up_off,
                            void* Y, int n, int Kp, const int* live, int T, void* stream);
 
 #ifdef __cplusplus

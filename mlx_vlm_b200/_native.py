@@ -113,14 +113,14 @@ LM_SIGNATURES = {
     "b200_device_check": (_I, [_I, C.POINTER(_I)]),
     "b200_lm_embed": (_I, [_P, _P, _F, _P, _I, _I, _I, _P]),
     "b200_lm_rope_table": (_I, [_P, _P, _P, _I, _I, _F, _P]),
-    "b200_lm_norm_rows": (_I, [_P, _L, _P, _I, _P, _F, _F, _P, _L, _I, _P, _I, _I, _I, _P]),
+    "b200_lm_norm_rows": (_I, [_P, _L, _P, _I, _P, _F, _F, _P, _L, _I, _P, _I, _I, _I, _I, _P]),
     "b200_lm_latent_post": (_I, [_P, _L, _P, _P, _F, _P, _L, _P, _I, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P]),
     "b200_lm_rope_q": (_I, [_P, _L, _I, _I, _P, _L, _I, _I, _P, _I, _I, _I, _I, _I, _P]),
     "b200_lm_latent_attention": (_I, [_P, _L, _P, _I, _L, _L, _P, _P, _P, _L, _I, _I, _I, _F, _I, _I, _P, _I, _I, _P]),
     "b200_lm_router_topk": (_I, [_P, _L, _I, _I, _P, _P, _I, _P]),
-    "b200_lm_router_group_topk": (_I, [_P, _L, _P, _I, _I, _I, _I, _P, _P, _I, _P]),
-    "b200_lm_residual_rows": (_I, [_P, _L, _P, _I, _P, _L, _P, _L, _P, _P, _L, _I, _I, _P]),
-    "b200_lm_residual_norm_rows": (_I, [_P, _L, _P, _I, _P, _L, _P, _L, _P, _P, _L, _P, _F, _F, _I, _P, _L, _I, _I, _P]),
+    "b200_lm_router_group_topk": (_I, [_P, _L, _P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _P]),
+    "b200_lm_residual_rows": (_I, [_P, _L, _P, _I, _P, _L, _P, _L, _P, _F, _P, _L, _I, _I, _P]),
+    "b200_lm_residual_norm_rows": (_I, [_P, _L, _P, _I, _P, _L, _P, _L, _P, _P, _L, _P, _F, _F, _I, _P, _L, _I, _F, _I, _I, _P]),
     "b200_lm_moe_group": (_I, [_P, _I, _I, _P, _L, _P, _P]),
     "b200_lm_gemm_rows": (_I, [_P, _L, _L, _P, _L, _L, _P, _P, _L, _L, _P, _L, _P, _I, _I, _I, _I, _I, _I, _F, _I,
                                _I, _I, _P]),
@@ -137,17 +137,19 @@ LM_SIGNATURES = {
     "b200_f32_split": (_I, [_P, _L, _P, _L, _I, _I, _I, _P]),
     "b200_lm_advance_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _P]),
     # csrc/mixer_ops.cu
-    "b200_lm_short_conv": (_I, [_P, _L, _P, _P, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _P]),
-    "b200_lm_qkv_post": (_I, [_P, _L, _P, _L, _P, _L, _P, _I, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
-    "b200_lm_sink_attention": (_I, [_P, _L, _P, _I, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _P, _I, _I,
+    "b200_lm_short_conv": (_I, [_P, _L, _P, _P, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _P]),
+    "b200_lm_token_shift": (_I, [_P, _L, _P, _P, _L, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "b200_lm_qkv_post": (_I, [_P, _L, _P, _L, _P, _L, _P, _I, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _I, _F, _I, _P,
+                              _P, _L, _P, _L, _I, _P]),
+    "b200_lm_sink_attention": (_I, [_P, _L, _P, _I, _L, _L, _P, _P, _P, _L, _P, _I, _I, _I, _I, _F, _I, _I, _F, _I, _P, _I, _I,
                                     _P]),
     "b200_lm_linear_state": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F,
-                                  _P, _P, _L, _P, _P, _P, _L, _I, _I, _P, _P, _I, _P]),
+                                  _P, _P, _L, _P, _P, _P, _L, _I, _I, _P, _P, _L, _P, _P, _I, _P]),
     "b200_lm_heads_to_bf16": (_I, [_P, _L, _I, _I, _P, _I, _I, _P]),
-    "b200_lm_sink_softmax_bf16": (_I, [_P, _L, _P, _I, _P, _F, _I, _I, _I, _P, _L, _I, _I, _P]),
+    "b200_lm_sink_softmax_bf16": (_I, [_P, _L, _P, _I, _P, _F, _I, _I, _I, _F, _I, _I, _I, _P, _L, _I, _I, _P]),
     "b200_lm_head_post": (_I, [_P, _L, _P, _L, _P, _I, _F, _I, _I, _I, _I, _I, _F, _P, _L, _I, _I, _P]),
-    "b200_lm_glu_clamp": (_I, [_P, _L, _P, _L, _F, _F, _F, _P, _L, _I, _I, _P]),
-    "b200_lm_glu_clamp_bf16": (_I, [_P, _L, _P, _L, _F, _F, _F, _P, _I, _I, _P, _I, _P]),
+    "b200_lm_glu_clamp": (_I, [_P, _L, _P, _L, _F, _F, _F, _F, _P, _L, _I, _I, _P]),
+    "b200_lm_glu_clamp_bf16": (_I, [_P, _L, _P, _L, _F, _F, _F, _F, _P, _I, _I, _P, _I, _P]),
 }
 SIGNATURES.update(LM_SIGNATURES)
 

@@ -63,7 +63,8 @@ __global__ void rope_table_kernel(const int* __restrict__ pos, const double* __r
 // ---------------------------------------------------------------------------------------------------------
 // RMS norm of y's rows (optionally the weighted sum of `top` rows of a scattered buffer), weight (w_offset + w),
 // then either out = norm or x += norm.  rows: optional gather list for the input row.  center: the row's mean is
-// taken off first and the root mean square is that of the deviations (a layer norm without bias).
+// taken off first and the root mean square is that of the deviations (a layer norm without bias).  groups > 1: the row
+// is `groups` equal consecutive parts, each divided by its own root mean square (no centering then).
 struct NormP {
   const float* y; long ldy;
   const float* wgt; int top;          // combine: y row = sum_s wgt[t*top+s] * y[(t*top+s)]
@@ -79,6 +80,8 @@ struct NormP {
   const bf16* ls;
   const float* shared; long lds;
   const float* sgate; long ldsg;
+  int groups;                         // parts of the row with a root mean square of their own (1: the whole row)
+  float mult;                         // the residual update is scaled by this number as well (beside ls)
 };
 __global__ void norm_rows_kernel(NormP p) {
   extern __shared__ float sm[];
@@ -99,11 +102,29 @@ __global__ void norm_rows_kernel(NormP p) {
     if (p.res) {                      // the same arithmetic, in the same order, as residual_rows_kernel
       if (p.shared) v = fmaf(sg, p.shared[r * p.lds + i], v);
       float* o = p.res + r * p.ldr + i;
-      v = fmaf(p.ls ? bf2f(p.ls[i]) : 1.f, v, *o);
+      v = fmaf((p.ls ? bf2f(p.ls[i]) : 1.f) * p.mult, v, *o);
       *o = v;
     }
     row[i] = v;
     ss += p.center ? v : v * v;
+  }
+  if (p.groups > 1) {                 // a warp per part, lanes striding it: the order of the sum is fixed by the part's size
+    float* ginv = red + 32;           // groups
+    __syncthreads();
+    const int span = p.N / p.groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int g = warp; g < p.groups; g += nw) {
+      float a = 0.f;
+      for (int i = lane; i < span; i += 32) { const float v = row[g * span + i]; a = fmaf(v, v, a); }
+      a = warp_sum(a);
+      if (lane == 0) ginv[g] = 1.0f / sqrtf(a / (float)span + p.eps);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.N; i += blockDim.x) {
+      const float v = row[i] * ginv[i / span] * (p.w_offset + bf2f(p.w[i]));
+      float* o = p.x + (long)t * p.ldx + i;
+      *o = p.add ? *o + v : v;
+    }
+    return;
   }
   float tot = block_sum(ss, red), mean = 0.f;
   if (p.center) {                     // two passes over the staged row: mean, then the squared deviations
@@ -375,9 +396,10 @@ __global__ void router_topk_kernel(const float* __restrict__ z, long ldz, int E,
 // largest c (its only c when a group is one expert), and only experts of the `keep` best groups can be chosen (the
 // others count as minus infinity); the `top` largest c are chosen (lowest index wins a tie) and weighted by their s,
 // divided by the sum of the chosen s (+ 1e-20).  A warp per token; the choice scores of a token sit in shared memory.
+// softmax: s = softmax(z) over all experts instead of the sigmoid; group_max: a group's score is its largest c.
 __global__ void router_group_topk_kernel(const float* __restrict__ z, long ldz, const bf16* __restrict__ corr, int E,
-                                         int top, int n_groups, int keep, int* __restrict__ idx,
-                                         float* __restrict__ wgt, int T) {
+                                         int top, int n_groups, int keep, int softmax, int group_max,
+                                         int* __restrict__ idx, float* __restrict__ wgt, int T) {
   extern __shared__ float sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const int t = blockIdx.x * nw + warp;
@@ -385,7 +407,17 @@ __global__ void router_group_topk_kernel(const float* __restrict__ z, long ldz, 
   float* c = sm + (long)warp * (E + n_groups);      // [E] choice scores, then [n_groups] group scores
   float* gs = c + E;
   const float* zr = z + (long)t * ldz;
-  for (int e = lane; e < E; e += 32) c[e] = 1.0f / (1.0f + expf(-zr[e])) + (corr ? bf2f(corr[e]) : 0.f);
+  float zmax = 0.f, zinv = 1.f;
+  if (softmax) {
+    float a = -INFINITY;
+    for (int e = lane; e < E; e += 32) a = fmaxf(a, zr[e]);
+    zmax = warp_max(a);
+    float b = 0.f;
+    for (int e = lane; e < E; e += 32) b += expf(zr[e] - zmax);
+    zinv = 1.0f / warp_sum(b);
+  }
+  for (int e = lane; e < E; e += 32)
+    c[e] = (softmax ? expf(zr[e] - zmax) * zinv : 1.0f / (1.0f + expf(-zr[e]))) + (corr ? bf2f(corr[e]) : 0.f);
   __syncwarp();
   if (n_groups > 1 && keep < n_groups) {
     const int per = E / n_groups;
@@ -395,7 +427,7 @@ __global__ void router_group_topk_kernel(const float* __restrict__ z, long ldz, 
         const float v = c[g * per + i];
         if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
       }
-      gs[g] = per > 1 ? a + b : a;
+      gs[g] = (per > 1 && !group_max) ? a + b : a;
     }
     __syncwarp();
     for (int s = 0; s < keep; ++s) {                  // the best group leaves the contest with a mark: NaN-free +inf
@@ -433,7 +465,7 @@ __global__ void router_group_topk_kernel(const float* __restrict__ z, long ldz, 
     }
     if (bi >= E) bi = 0;                              // fewer choosable experts than `top`: the host refuses that
     __syncwarp();
-    const float sc = 1.0f / (1.0f + expf(-zr[bi]));
+    const float sc = softmax ? expf(zr[bi] - zmax) * zinv : 1.0f / (1.0f + expf(-zr[bi]));
     denom += sc;
     if (lane == 0) { c[bi] = -INFINITY; idx[(long)t * top + s] = bi; wgt[(long)t * top + s] = sc; }
     __syncwarp();
@@ -448,7 +480,8 @@ __global__ void router_group_topk_kernel(const float* __restrict__ z, long ldz, 
 //                                                                    + sigmoid(sgate[t]) shared[t] )   (if shared)
 __global__ void residual_rows_kernel(const float* __restrict__ y, long ldy, const float* __restrict__ wgt, int top,
                                      const float* __restrict__ shared, long lds, const float* __restrict__ sgate,
-                                     long ldsg, const bf16* __restrict__ ls, float* __restrict__ x, long ldx, int N) {
+                                     long ldsg, const bf16* __restrict__ ls, float mult, float* __restrict__ x, long ldx,
+                                     int N) {
   const long t = blockIdx.x;
   const float sg = shared ? (sgate ? 1.0f / (1.0f + expf(-sgate[t * ldsg])) : 1.f) : 0.f;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < N; i += blockDim.x * gridDim.y) {
@@ -461,7 +494,7 @@ __global__ void residual_rows_kernel(const float* __restrict__ y, long ldy, cons
     }
     if (shared) v = fmaf(sg, shared[t * lds + i], v);
     float* o = x + t * ldx + i;
-    *o = fmaf(ls ? bf2f(ls[i]) : 1.f, v, *o);
+    *o = fmaf((ls ? bf2f(ls[i]) : 1.f) * mult, v, *o);
   }
 }
 
@@ -504,7 +537,7 @@ struct GemmRowsP {
   const int* count;                      // per batch: rows (device); NULL: M rows, no list
   int x_div;
   int M, N, K;
-  int epi; float epi_param;              // 0 none, 1 relu^2, 2 param * tanh(v / param), 3 added to the output, 4 v * param
+  int epi; float epi_param;              // 0 none, 1 relu^2, 2 param * tanh(v / param), 3 added to the output, 4 v * param, 5 gelu
   int round_x;
   int compact, n_batch;                  // compact: blockIdx.z counts the batches that HAVE rows (count[b] > 0) —
 };                                       // a decode step launches top x rows slices, not one per expert
@@ -534,6 +567,7 @@ __device__ __forceinline__ float gemm_epi(float v, int epi, float param) {
   if (epi == 1) { v = fmaxf(v, 0.f); return v * v; }
   if (epi == 2) return param * tanhf(v / param);
   if (epi == 4) return v * param;
+  if (epi == 5) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));    // the exact gelu
   return v;
 }
 // epi 3: the product is added to what the output row holds (a residual stream that accumulates in place)
@@ -743,7 +777,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemm_skinny_vec_kernel(GemmRows
 // Operands of the tensor-core products of a prompt step (bf16 serving mode; the products themselves are the
 // weight-major tcgen05 GEMM with fp32 output, b200_gemm_wt_f32):
 // rows of fp32 numbers -> bf16 rows padded with zeros to Kp columns; optional gather (src row = map[i] / div),
-// optional relu^2 before the rounding; with `dst_map` the kernel instead scatters fp32 rows (dst row = dst_map[i])
+// optional activation before the rounding (1: relu^2, 2: the exact gelu); with `dst_map` the kernel instead scatters fp32 rows (dst row = dst_map[i])
 __global__ void rows_to_bf16_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ map, int div,
                                     bf16* __restrict__ out, long ldo, int K, int Kp, int relu2) {
   const int i = blockIdx.x;
@@ -751,7 +785,8 @@ __global__ void rows_to_bf16_kernel(const float* __restrict__ X, long ldx, const
   const float* x = X + (long)(src < 0 ? 0 : (map ? src / div : src)) * ldx;
   for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
     float v = (k < K && src >= 0) ? x[k] : 0.f;
-    if (relu2) { v = fmaxf(v, 0.f); v *= v; }
+    if (relu2 == 1) { v = fmaxf(v, 0.f); v *= v; }
+    else if (relu2 == 2) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
     out[(long)i * ldo + k] = f2bf(v);
   }
 }
@@ -764,7 +799,10 @@ __global__ void rows_to_bf16x4_kernel(const float* __restrict__ X, long ldx, con
   for (int k = threadIdx.x * 4; k < Kp; k += blockDim.x * 4) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (k < K && src >= 0) v = *reinterpret_cast<const float4*>(x + k);
-    if (relu2) {
+    if (relu2 == 2) {
+      v.x = 0.5f * v.x * (1.0f + erff(v.x * 0.70710678118654752f)); v.y = 0.5f * v.y * (1.0f + erff(v.y * 0.70710678118654752f));
+      v.z = 0.5f * v.z * (1.0f + erff(v.z * 0.70710678118654752f)); v.w = 0.5f * v.w * (1.0f + erff(v.w * 0.70710678118654752f));
+    } else if (relu2 == 1) {
       v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
       v.x *= v.x; v.y *= v.y; v.z *= v.z; v.w *= v.w;
     }
@@ -1015,23 +1053,29 @@ int b200_lm_rope_table(const int* pos, const double* inv_freq, float* cs, int T,
 }
 
 int b200_lm_norm_rows(const float* y, long ldy, const float* wgt, int top, const void* w, float w_offset, float eps,
-                      float* x, long ldx, int add, const int* rows, int center, int T, int N, void* st) {
+                      float* x, long ldx, int add, const int* rows, int center, int groups, int T, int N, void* st) {
   B200_REQUIRE(y && w && x && T > 0 && N > 0, "lm_norm_rows: bad argument");
-  B200_REQUIRE((N + 32) * 4 <= 48 * 1024, "lm_norm_rows: rows of %d numbers do not fit shared memory", N);
-  NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, x, ldx, add, rows, N, center, nullptr, 0, nullptr, nullptr, 0, nullptr, 0};
-  norm_rows_kernel<<<T, T < 64 ? 1024 : 256, (N + 32) * sizeof(float), (cudaStream_t)st>>>(p);
+  if (groups < 1) groups = 1;
+  B200_REQUIRE(N % groups == 0 && groups <= 1024 && !(center && groups > 1), "lm_norm_rows: %d parts of a row of %d numbers", groups, N);
+  B200_REQUIRE((N + 32 + groups) * 4 <= 48 * 1024, "lm_norm_rows: rows of %d numbers do not fit shared memory", N);
+  NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, x, ldx, add, rows, N, center, nullptr, 0, nullptr, nullptr, 0, nullptr, 0,
+          groups, 1.f};
+  norm_rows_kernel<<<T, T < 64 ? 1024 : 256, (N + 32 + groups) * sizeof(float), (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
 
 int b200_lm_residual_norm_rows(const float* y, long ldy, const float* wgt, int top, const float* shared, long lds,
                                const float* sgate, long ldsg, const void* ls, float* res, long ldr, const void* w,
-                               float w_offset, float eps, int center, float* out, long ldo, int T, int N, void* st) {
+                               float w_offset, float eps, int center, float* out, long ldo, int groups, float mult,
+                               int T, int N, void* st) {
   B200_REQUIRE(y && res && w && out && T > 0 && N > 0 && (top == 0 || wgt), "lm_residual_norm_rows: bad argument");
-  B200_REQUIRE((N + 32) * 4 <= 48 * 1024, "lm_residual_norm_rows: rows of %d numbers do not fit shared memory", N);
+  if (groups < 1) groups = 1;
+  B200_REQUIRE(N % groups == 0 && groups <= 1024 && !(center && groups > 1), "lm_residual_norm_rows: %d parts of a row of %d numbers", groups, N);
+  B200_REQUIRE((N + 32 + groups) * 4 <= 48 * 1024, "lm_residual_norm_rows: rows of %d numbers do not fit shared memory", N);
   NormP p{y, ldy, wgt, wgt ? top : 0, (const bf16*)w, w_offset, eps, out, ldo, 0, nullptr, N, center,
-          res, ldr, (const bf16*)ls, shared, lds, sgate, ldsg};
-  norm_rows_kernel<<<T, T < 64 ? 1024 : 256, (N + 32) * sizeof(float), (cudaStream_t)st>>>(p);
+          res, ldr, (const bf16*)ls, shared, lds, sgate, ldsg, groups, mult};
+  norm_rows_kernel<<<T, T < 64 ? 1024 : 256, (N + 32 + groups) * sizeof(float), (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
@@ -1106,24 +1150,25 @@ int b200_lm_router_topk(const float* z, long ldz, int E, int top, int* idx, floa
 }
 
 int b200_lm_router_group_topk(const float* z, long ldz, const void* correction, int E, int top, int n_groups, int keep,
-                              int* idx, float* wgt, int T, void* st) {
+                              int softmax, int group_max, int* idx, float* wgt, int T, void* st) {
   B200_REQUIRE(z && idx && wgt && T > 0 && top > 0 && top <= E && E <= 2048, "lm_router_group_topk: bad argument");
   B200_REQUIRE(n_groups >= 1 && E % n_groups == 0 && keep >= 1 && keep <= n_groups,
                "lm_router_group_topk: %d experts in %d groups, %d kept", E, n_groups, keep);
   B200_REQUIRE(top <= (long)keep * (E / n_groups), "lm_router_group_topk: %d experts chosen among %d", top, keep * (E / n_groups));
   const int nw = 4;
   router_group_topk_kernel<<<cdiv(T, nw), nw * 32, (size_t)nw * (E + n_groups) * sizeof(float), (cudaStream_t)st>>>(
-      z, ldz, (const bf16*)correction, E, top, n_groups, keep, idx, wgt, T);
+      z, ldz, (const bf16*)correction, E, top, n_groups, keep, softmax, group_max, idx, wgt, T);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
 
 int b200_lm_residual_rows(const float* y, long ldy, const float* wgt, int top, const float* shared, long lds,
-                          const float* sgate, long ldsg, const void* ls, float* x, long ldx, int T, int N, void* st) {
+                          const float* sgate, long ldsg, const void* ls, float mult, float* x, long ldx, int T, int N,
+                          void* st) {
   B200_REQUIRE(y && x && T > 0 && N > 0 && (top == 0 || wgt), "lm_residual_rows: bad argument");
   const int by = T >= 64 ? 1 : (cdiv(N, 256) < 16 ? cdiv(N, 256) : 16);
   residual_rows_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(y, ldy, wgt, wgt ? top : 0, shared, lds, sgate, ldsg,
-                                                                  (const bf16*)ls, x, ldx, N);
+                                                                  (const bf16*)ls, mult, x, ldx, N);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

@@ -24,6 +24,17 @@ __device__ __forceinline__ void st_row(bf16* p, float v) { *p = f2bf(v); }
 __device__ __forceinline__ float sigmoid_exact(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float silu_exact(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float softplus_exact(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float glu_arg(float g, float cubic) { return cubic != 0.f ? g + cubic * g * g * g : g; }
+__device__ __forceinline__ float block_sum_fixed(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
 
 // ---------------------------------------------------------------------------------------------------------
 // short convolution: y[t][c] = act( bias[c] + sum_j w[c][j] * u[t - (taps - 1) + j][c] ), inputs before the step come from
@@ -36,6 +47,7 @@ struct ConvP {
   const int *slot, *pos, *first;
   int C, taps, act;
   const bf16* bias;                // [C] or NULL
+  int residual;                    // the input itself is added to the convolution's output (before the activation)
 };
 __global__ void short_conv_kernel(ConvP p) {
   const int t = blockIdx.x;
@@ -43,6 +55,7 @@ __global__ void short_conv_kernel(ConvP p) {
   const float* st = p.state + (long)p.slot[t] * p.slot_stride;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.C; c += blockDim.x * gridDim.y) {
     float a = p.bias ? bf2f(p.bias[c]) : 0.f;
+    if (p.residual) a += p.U[(long)t * p.ldu + c];
     for (int j = 0; j < p.taps; ++j) {
       const int lag = p.taps - 1 - j;
       float u = 0.f;
@@ -70,6 +83,39 @@ __global__ void conv_state_kernel(ConvP p, const int* __restrict__ seqs) {
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// token shift: M[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s] for each of n_mix mixing vectors; h[t - 1] of a sequence's
+// first token of the step is the slot's kept row (zeros at position 0).  The slot then keeps the sequence's last
+// input: by the thread that read it when the sequence brings one token (a decode step), else by a second launch.
+struct ShiftP {
+  const float* h; long ldh;
+  const bf16* mu;                  // [n_mix][C]
+  float* M; long ldm, mix_stride;  // [n_mix][T][C]
+  float* state; long slot_stride;  // per slot [C]
+  const int *slot, *pos, *first;
+  int C, n_mix, single;            // single: every sequence of the step is one token
+};
+__global__ void token_shift_kernel(ShiftP p) {
+  const int t = blockIdx.x;
+  const bool head = p.first[t] == t;
+  float* st = p.state + (long)p.slot[t] * p.slot_stride;
+  const bool fresh = p.pos[t] == 0;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.C; c += blockDim.x * gridDim.y) {
+    const float x = p.h[(long)t * p.ldh + c];
+    const float prev = head ? (fresh ? 0.f : st[c]) : p.h[(long)(t - 1) * p.ldh + c];
+    const float d = prev - x;
+    for (int s = 0; s < p.n_mix; ++s)
+      p.M[(long)s * p.mix_stride + (long)t * p.ldm + c] = fmaf(d, bf2f(p.mu[(long)s * p.C + c]), x);
+    if (p.single) st[c] = x;
+  }
+}
+__global__ void token_shift_state_kernel(ShiftP p, const int* __restrict__ seqs) {
+  const int start = seqs[2 * blockIdx.x], rows = seqs[2 * blockIdx.x + 1];
+  float* st = p.state + (long)p.slot[start] * p.slot_stride;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < p.C; c += blockDim.x * gridDim.y)
+    st[c] = p.h[(long)(start + rows - 1) * p.ldh + c];
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // rotary on q (in place) and k, and the cache rows of the step: cache[slot][pos] = [k of every kv head | v ...]
 template <typename CT>
 struct QkvPostP {
@@ -80,11 +126,39 @@ struct QkvPostP {
   const int *slot, *pos;
   const float2* cs;                // [T][rot_dims / 2]
   int H, G, dim, vdim, rot_dims;
+  // optional steps in front of the rotation and the cache write (all NULL / 0: none)
+  const bf16 *qn_w, *kn_w;         // [H dim], [G dim]: RMS norm over the WHOLE query / key projection, times these
+  float eps;
+  int v_unit;                      // every value head is divided by its root mean square (eps inside the root)
+  float qt_coef; int qt_every;     // queries times 1 + coef ln(floor((pos + 1) / every) + 1)
+  const bf16* vmix;                // one number lam: v <- (1 - lam) v + lam v_first (after the value norm)
+  const float* v_first; long ldvf; // [T][G vdim]
+  float* v_keep; long ldvk;        // [T][G vdim] or NULL: the values as cached, in fp32 (a later layer mixes with them)
 };
 template <typename CT>
 __global__ void qkv_post_kernel(QkvPostP<CT> p) {
+  __shared__ float red[32];
   const int t = blockIdx.x, half = p.rot_dims / 2;
   float* q = p.Q + (long)t * p.ldq;
+  const float* k = p.K + (long)t * p.ldk;
+  float k_inv = 1.f;
+  if (p.qn_w || p.qt_every > 0) {              // queries: the norm over all heads at once, then the temperature
+    float q_mul = 1.f;
+    if (p.qn_w) {
+      float ss = 0.f;
+      for (int e = threadIdx.x; e < p.H * p.dim; e += blockDim.x) ss = fmaf(q[e], q[e], ss);
+      q_mul = 1.0f / sqrtf(block_sum_fixed(ss, red) / (float)(p.H * p.dim) + p.eps);
+    }
+    if (p.qt_every > 0) q_mul *= 1.0f + p.qt_coef * logf((float)((p.pos[t] + 1) / p.qt_every) + 1.0f);
+    for (int e = threadIdx.x; e < p.H * p.dim; e += blockDim.x) q[e] = q[e] * q_mul * (p.qn_w ? bf2f(p.qn_w[e]) : 1.f);
+    __syncthreads();
+  }
+  if (p.kn_w) {
+    float ss = 0.f;
+    for (int e = threadIdx.x; e < p.G * p.dim; e += blockDim.x) ss = fmaf(k[e], k[e], ss);
+    k_inv = 1.0f / sqrtf(block_sum_fixed(ss, red) / (float)(p.G * p.dim) + p.eps);
+  }
+  auto kn = [&](int e) { return p.kn_w ? k[e] * k_inv * bf2f(p.kn_w[e]) : k[e]; };
   for (int e = threadIdx.x; e < p.H * half; e += blockDim.x) {
     const int h = e / half, i = e % half;
     const float2 a = p.cs[(long)t * half + i];
@@ -94,23 +168,42 @@ __global__ void qkv_post_kernel(QkvPostP<CT> p) {
     r[i + half] = hi * a.x + lo * a.y;
   }
   CT* row = p.cache + (long)p.slot[t] * p.slot_stride + (long)p.pos[t] * p.tok_stride;
-  const float* k = p.K + (long)t * p.ldk;
   for (int e = threadIdx.x; e < p.G * p.dim; e += blockDim.x) {
     const int i = e % p.dim;
     float v;
     if (i < half) {
       const float2 a = p.cs[(long)t * half + i];
-      v = k[e] * a.x - k[e + half] * a.y;
+      v = kn(e) * a.x - kn(e + half) * a.y;
     } else if (i < p.rot_dims) {
       const float2 a = p.cs[(long)t * half + i - half];
-      v = k[e] * a.x + k[e - half] * a.y;
+      v = kn(e) * a.x + kn(e - half) * a.y;
     } else {
-      v = k[e];
+      v = kn(e);
     }
     st_row(row + e, v);
   }
   const float* v = p.V + (long)t * p.ldv;
-  for (int e = threadIdx.x; e < p.G * p.vdim; e += blockDim.x) st_row(row + p.G * p.dim + e, v[e]);
+  if (!p.v_unit && !p.vmix && !p.v_keep) {
+    for (int e = threadIdx.x; e < p.G * p.vdim; e += blockDim.x) st_row(row + p.G * p.dim + e, v[e]);
+    return;
+  }
+  const float lam = p.vmix ? bf2f(*p.vmix) : 0.f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g < p.G; g += nw) {         // a warp per value head
+    float inv = 1.f;
+    if (p.v_unit) {
+      float ss = 0.f;
+      for (int i = lane; i < p.vdim; i += 32) { const float a = v[g * p.vdim + i]; ss = fmaf(a, a, ss); }
+      inv = 1.0f / sqrtf(warp_sum(ss) / (float)p.vdim + p.eps);
+    }
+    for (int i = lane; i < p.vdim; i += 32) {
+      const int e = g * p.vdim + i;
+      float a = v[e] * inv;
+      if (p.vmix) a = (1.0f - lam) * a + lam * p.v_first[(long)t * p.ldvf + e];
+      if (p.v_keep) p.v_keep[(long)t * p.ldvk + e] = a;
+      st_row(row + p.G * p.dim + e, a);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -132,7 +225,11 @@ struct SinkAttnP {
   int chunk, window;
   float* part; int n_split;        // n_split > 1: [T][H][n_split][vdim + 2] = (acc.., max, sum)
   int vec;                         // key and value columns of every row start on 16-byte boundaries and are whole
-};                                 // 16-byte vectors: rows are staged with 16-byte loads
+                                   // 16-byte vectors: rows are staged with 16-byte loads
+  float bias_exp;                  // > 0: slope_h (query position - key position) is taken off the score of head h,
+                                   // slope_h = 2^(-bias_exp (h + 1) / H)
+  int unit_sink;                   // the denominator also holds exp(0) = 1 (a sink logit of zero, no tensor)
+};
 template <typename CT>
 __global__ void sink_attention_kernel(SinkAttnP<CT> p) {
   extern __shared__ float sm[];
@@ -160,6 +257,8 @@ __global__ void sink_attention_kernel(SinkAttnP<CT> p) {
   const int per_lane = (vdim + 31) / 32;
   float m = -INFINITY, l = 0.f;
   if (p.sink && blockIdx.z == 0 && live) { m = bf2f(p.sink[h]); l = 1.f; }
+  if (p.unit_sink && blockIdx.z == 0 && live) { m = 0.f; l = 1.f; }
+  const float slope = p.bias_exp > 0.f ? exp2f(-p.bias_exp * (float)(h + 1) / (float)p.H) : 0.f;
   float acc[8];                              // vdim <= 256
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
@@ -217,7 +316,7 @@ __global__ void sink_attention_kernel(SinkAttnP<CT> p) {
       } else {
         for (int i = 0; i < dim; ++i) a = fmaf(qr[i], kr[i], a);
       }
-      s = a * p.scale;
+      s = a * p.scale - slope * (float)(ps - (k0 + lane));
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);       // nothing seen yet: exp(-inf) = 0
@@ -320,6 +419,9 @@ struct StateP {
   int delta;
   int dt_in;                        // state-space form: beta = softplus(a[t][h] + dt_bias[h]) (the step size) and u = beta v
   const bf16* skip;                 // [H] or NULL: o += skip[h] v
+  // decay per key channel (the template's CHAN; always prepared):  o = S^T q + (sum_i q_i bonus_i k_i) v  with S the state
+  // BEFORE the token, then  S <- diag(w) S + k v^T;  wdec [T][H dim] holds w, kq_in the bracket
+  const float* wdec; long ldw;
 };
 // The per-token work of a prompt step in one parallel pass: q, k activated and scaled to unit length (a warp per
 // token and q/k head, the same order of sums as the walk's own staging), k . q, the decay and beta of every head.
@@ -335,6 +437,10 @@ struct StatePrepP {
   const bf16 *A_log, *dt_bias;
   const float* b; long ldb;
   int dt_in;
+  // decay per key channel: wraw [T][H dim] -> wn = exp(-exp(wraw)); kq = sum_i q_i bonus_i k_i; no dec / bet
+  const float* wraw; long ldwr;
+  float* wn;
+  const bf16* bonus;                // [H][dim]
 };
 __global__ void state_prep_kernel(StatePrepP p) {
   const long t = blockIdx.x;
@@ -361,10 +467,14 @@ __global__ void state_prep_kernel(StatePrepP p) {
       if (p.act) { a = silu_exact(a); b = silu_exact(b); }
       a *= ik; b *= iq;
       ko[i] = a; qo[i] = b;
-      dot = fmaf(a, b, dot);
+      dot = p.wraw ? fmaf(a * b, bf2f(p.bonus[(long)hk * p.dim + i]), dot) : fmaf(a, b, dot);
     }
     dot = warp_sum(dot);
     if (lane == 0) p.kq[t * p.Hk + hk] = dot;
+  }
+  if (p.wraw) {
+    for (int e = threadIdx.x; e < p.H * p.dim; e += blockDim.x) p.wn[t * ((long)p.H * p.dim) + e] = expf(-expf(p.wraw[t * p.ldwr + e]));
+    return;
   }
   for (int h = threadIdx.x; h < p.H; h += blockDim.x) {
     const float dt = p.decay_const ? 0.f : softplus_exact(p.a[t * p.lda + h] + bf2f(p.dt_bias[h]));
@@ -373,7 +483,7 @@ __global__ void state_prep_kernel(StatePrepP p) {
   }
 }
 
-template <int P, bool DELTA>
+template <int P, bool DELTA, bool CHAN>
 __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
   // Tokens are staged CT at a time.  The raw q, k, v, decay and beta inputs of the NEXT group are requested from
   // global memory into registers before the current group is walked, so their latency hides behind the walk.
@@ -384,7 +494,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
   constexpr int CB = LS_THREADS / P, LD = P * LS_RS, DKP = P * LS_R;
   constexpr int CT = P >= 32 ? LS_CT / 2 : LS_CT;       // tokens per group: the staged rows fit static shared memory
   constexpr int NQK = (CT * DKP + LS_THREADS - 1) / LS_THREADS, NV = (CT * CB + LS_THREADS - 1) / LS_THREADS;
-  __shared__ __align__(16) float ks[CT][LD], qs[CT][LD];
+  __shared__ __align__(16) float ks[CT][LD], qs[CT][LD], ws[CHAN ? CT : 1][CHAN ? LD : 4];
   __shared__ float vs[CT][CB];
   __shared__ float dec[CT], bet[CT], kq[CT];
   const int start = p.seqs[2 * blockIdx.x], rows = p.seqs[2 * blockIdx.x + 1];
@@ -401,7 +511,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
 #pragma unroll
     for (int i = 0; i < LS_R; ++i) S[i] = 0.f;
   }
-  float rk[NQK], rq[NQK], rv[NV], ra = 0.f, rb = 0.f, rkq = 0.f;
+  float rk[NQK], rq[NQK], rw[CHAN ? NQK : 1], rv[NV], ra = 0.f, rb = 0.f, rkq = 0.f;
   const bool raw = p.kq_in == nullptr, act_qk = raw && p.act;
   auto request = [&](int c0) {               // raw inputs of tokens c0 .. c0 + CT - 1 (zeros past the end)
     const int nc = min(CT, rows - c0);
@@ -412,6 +522,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       const long t = start + c0 + tk;
       rk[n] = ok ? p.k[t * p.ldk + (long)hk * p.dim + i] : 0.f;
       rq[n] = ok ? p.q[t * p.ldq + (long)hk * p.dim + i] : 0.f;
+      if (CHAN) rw[n] = ok ? p.wdec[t * p.ldw + (long)h * p.dim + i] : 0.f;
     }
 #pragma unroll
     for (int n = 0; n < NV; ++n) {
@@ -420,7 +531,9 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     }
     if ((int)threadIdx.x < nc) {
       const long t = start + c0 + threadIdx.x;
-      if (p.kq_in) {
+      if (CHAN) {
+        rkq = p.kq_in[t * (p.H / p.rep) + hk];
+      } else if (p.kq_in) {
         ra = p.dec_in[t * p.H + h]; rb = p.bet_in[t * p.H + h]; rkq = p.kq_in[t * (p.H / p.rep) + hk];
       } else {
         if (!p.decay_const) ra = p.a[t * p.lda + h];
@@ -441,6 +554,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       if (e < CT * DKP) {
         ks[tk][(i / LS_R) * LS_RS + (i % LS_R)] = act_qk ? silu_exact(rk[n]) : rk[n];
         qs[tk][(i / LS_R) * LS_RS + (i % LS_R)] = act_qk ? silu_exact(rq[n]) : rq[n];
+        if (CHAN) ws[tk][(i / LS_R) * LS_RS + (i % LS_R)] = rw[n];
       }
     }
 #pragma unroll
@@ -484,12 +598,29 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     float* op = p.out + (long)(start + c0) * p.ldo + (long)h * p.vdim + col;
     const float* kp = &ks[0][r * LS_RS];
     const float* qp = &qs[0][r * LS_RS];
+    const float* wp = &ws[0][CHAN ? r * LS_RS : 0];
 #pragma unroll(DELTA ? 1 : 4)
     for (int tk = 0; tk < nc; ++tk, op += p.ldo, kp += LD, qp += LD) {
       const float4 k0 = *reinterpret_cast<const float4*>(kp), k1 = *reinterpret_cast<const float4*>(kp + 4);
       const float4 q0 = *reinterpret_cast<const float4*>(qp), q1 = *reinterpret_cast<const float4*>(qp + 4);
       const float k_[LS_R] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
       const float q_[LS_R] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+      if (CHAN) {                  // the output reads the state before the token; every row has its own decay
+        const float4 w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + 4);
+        const float w_[LS_R] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        wp += LD;
+        float b0 = 0.f, b1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < LS_R; i += 2) { b0 = fmaf(S[i], q_[i], b0); b1 = fmaf(S[i + 1], q_[i + 1], b1); }
+        float dq = b0 + b1;
+#pragma unroll
+        for (int o = 1; o < P; o <<= 1) dq += __shfl_xor_sync(0xffffffffu, dq, o);
+        const float vin = vs[tk][cj];
+        if (r == 0 && valid) *op = fmaf(vin, kq[tk], dq);
+#pragma unroll
+        for (int i = 0; i < LS_R; ++i) S[i] = fmaf(k_[i], vin, w_[i] * S[i]);
+        continue;
+      }
       const float d = dec[tk];
       float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;       // two running sums per dot: short dependency chains
 #pragma unroll
@@ -584,19 +715,21 @@ __global__ void head_post_kernel(HeadPostP p) {
   }
 }
 
-// gated feed-forward activation with clamps: g = min(a, lim), u = clamp(b, -lim, lim), y = g sigmoid(alpha g) (u + up_off)
-// (lim = +inf, alpha = 1, up_off = 0: the plain silu-gated unit)
+// gated feed-forward activation with clamps: g = min(a, lim), u = clamp(b, -lim, lim),
+// y = g sigmoid(alpha (g + cubic g^3)) (u + up_off)
+// (lim = +inf, alpha = 1, cubic = 0, up_off = 0: the plain silu-gated unit; alpha = 2 sqrt(2 / pi), cubic = 0.044715: the
+// tanh form of gelu on the gate, since 0.5 (1 + tanh a) = sigmoid(2 a))
 __global__ void glu_clamp_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
-                                 float alpha, float up_off, float* __restrict__ Y, long ldy, int n) {
+                                 float alpha, float cubic, float up_off, float* __restrict__ Y, long ldy, int n) {
   const int t = blockIdx.x, i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float g = fminf(G[(long)t * ldg + i], lim);
   const float u = fminf(fmaxf(U[(long)t * ldu + i], -lim), lim);
-  Y[(long)t * ldy + i] = g * sigmoid_exact(alpha * g) * (u + up_off);
+  Y[(long)t * ldy + i] = g * sigmoid_exact(alpha * glu_arg(g, cubic)) * (u + up_off);
 }
 // the same, four columns per thread (rows of whole, aligned 16-byte vectors)
 __global__ void glu_clamp4_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
-                                  float alpha, float up_off, float* __restrict__ Y, long ldy, int n) {
+                                  float alpha, float cubic, float up_off, float* __restrict__ Y, long ldy, int n) {
   const int t = blockIdx.x, i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
   const float4 a = *reinterpret_cast<const float4*>(G + (long)t * ldg + i);
@@ -606,14 +739,14 @@ __global__ void glu_clamp4_kernel(const float* __restrict__ G, long ldg, const f
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const float g = fminf(gs[e], lim), u = fminf(fmaxf(us[e], -lim), lim);
-    y[e] = g * sigmoid_exact(alpha * g) * (u + up_off);
+    y[e] = g * sigmoid_exact(alpha * glu_arg(g, cubic)) * (u + up_off);
   }
   *reinterpret_cast<float4*>(Y + (long)t * ldy + i) = make_float4(y[0], y[1], y[2], y[3]);
 }
 
 // the same, written as the bf16 operand rows of the next tensor-core product (zero-padded to Kp columns)
 __global__ void glu_clamp_bf16_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
-                                      float alpha, float up_off, bf16* __restrict__ Y, int n, int Kp,
+                                      float alpha, float cubic, float up_off, bf16* __restrict__ Y, int n, int Kp,
                                       const int* __restrict__ live) {
   const long t = blockIdx.x;
   const bool pad = live && live[t] < 0;          // a padding row of a sorted segment: zeros, its inputs are not read
@@ -621,7 +754,7 @@ __global__ void glu_clamp_bf16_kernel(const float* __restrict__ G, long ldg, con
     float y = 0.f;
     if (i < n && !pad) {
       const float g = fminf(G[t * ldg + i], lim), u = fminf(fmaxf(U[t * ldu + i], -lim), lim);
-      y = g * sigmoid_exact(alpha * g) * (u + up_off);
+      y = g * sigmoid_exact(alpha * glu_arg(g, cubic)) * (u + up_off);
     }
     Y[t * Kp + i] = f2bf(y);
   }
@@ -629,7 +762,7 @@ __global__ void glu_clamp_bf16_kernel(const float* __restrict__ G, long ldg, con
 
 // four columns per thread (rows of whole, aligned 16-byte vectors; n and Kp multiples of 4)
 __global__ void glu_clamp_bf16x4_kernel(const float* __restrict__ G, long ldg, const float* __restrict__ U, long ldu, float lim,
-                                        float alpha, float up_off, bf16* __restrict__ Y, int n, int Kp,
+                                        float alpha, float cubic, float up_off, bf16* __restrict__ Y, int n, int Kp,
                                         const int* __restrict__ live) {
   const long t = blockIdx.x;
   const bool pad = live && live[t] < 0;
@@ -642,7 +775,7 @@ __global__ void glu_clamp_bf16x4_kernel(const float* __restrict__ G, long ldg, c
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float g = fminf(gs[e], lim), u = fminf(fmaxf(us[e], -lim), lim);
-        y[e] = g * sigmoid_exact(alpha * g) * (u + up_off);
+        y[e] = g * sigmoid_exact(alpha * glu_arg(g, cubic)) * (u + up_off);
       }
     }
     const __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
@@ -665,19 +798,10 @@ __global__ void heads_to_bf16_kernel(const float* __restrict__ q, long ldq, int 
   const float* x = q + (long)t * ldq + r * dim;
   for (int k = threadIdx.x; k < Kp; k += blockDim.x) out[(long)i * Kp + k] = f2bf(k < dim ? x[k] : 0.f);
 }
-__device__ __forceinline__ float block_sum_fixed(float v, float* red) {
-  v = warp_sum(v);
-  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
-  __syncthreads();
-  if (l == 0) red[w] = v;
-  __syncthreads();
-  float t = 0.f;
-  for (int i = 0; i < nw; ++i) t += red[i];
-  return t;
-}
 __global__ void sink_softmax_bf16_kernel(const float* __restrict__ S, long lds, const int* __restrict__ pos, int rep,
                                          const bf16* __restrict__ sink, float scale, int chunk, int window, int key0,
-                                         bf16* __restrict__ P, long ldp, int Sp) {
+                                         float bias_exp, int head0, int H, int unit_sink, bf16* __restrict__ P, long ldp,
+                                         int Sp) {
   __shared__ float red[32];
   const long r = blockIdx.x;
   const int ps = pos[r / rep];
@@ -686,20 +810,23 @@ __global__ void sink_softmax_bf16_kernel(const float* __restrict__ S, long lds, 
   if (window > 0) lo = max(lo, ps - window + 1);
   const int j0 = lo - key0, j1 = ps - key0;            // visible columns j0 .. j1
   const float* s = S + r * lds;
-  const float sk = sink ? bf2f(sink[r % rep]) : -INFINITY;
+  const float sk = sink ? bf2f(sink[r % rep]) : (unit_sink ? 0.f : -INFINITY);
+  const float slope = bias_exp > 0.f ? exp2f(-bias_exp * (float)(head0 + (int)(r % rep) + 1) / (float)H) : 0.f;
+  // the score of column j: scale s_j - slope (distance to the query); j1 - j is that distance
+  auto sc = [&](int j) { return s[j] * scale - slope * (float)(j1 - j); };
   float m = sk;
-  for (int j = j0 + threadIdx.x; j <= j1; j += blockDim.x) m = fmaxf(m, s[j] * scale);
+  for (int j = j0 + threadIdx.x; j <= j1; j += blockDim.x) m = fmaxf(m, sc(j));
   m = warp_max(m);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
   __syncthreads();
   for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m = fmaxf(m, red[i]);
   float sum = 0.f;
-  for (int j = j0 + threadIdx.x; j <= j1; j += blockDim.x) sum += expf(s[j] * scale - m);
-  const float tot = block_sum_fixed(sum, red) + (sink ? expf(sk - m) : 0.f);
+  for (int j = j0 + threadIdx.x; j <= j1; j += blockDim.x) sum += expf(sc(j) - m);
+  const float tot = block_sum_fixed(sum, red) + ((sink || unit_sink) ? expf(sk - m) : 0.f);
   const float inv = 1.0f / tot;
   for (int j = threadIdx.x; j < Sp; j += blockDim.x)
-    P[r * ldp + j] = f2bf((j >= j0 && j <= j1) ? expf(s[j] * scale - m) * inv : 0.f);
+    P[r * ldp + j] = f2bf((j >= j0 && j <= j1) ? expf(sc(j) - m) * inv : 0.f);
 }
 
 unsigned long long g_sink_attr_f32 = 0, g_sink_attr_bf16 = 0;
@@ -713,10 +840,10 @@ extern "C" {
 
 int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
                        const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
-                       int act, const void* bias, int T, void* st) {
+                       int act, const void* bias, int residual, int T, void* st) {
   B200_REQUIRE(U && w && Y && (state || taps == 1) && slot && pos && first && seqs && T > 0 && n_seq > 0 && C > 0 && taps > 0,
                "lm_short_conv: bad argument");     // one tap keeps nothing between steps
-  ConvP p{U, ldu, (const bf16*)w, Y, ldy, state, slot_stride, slot, pos, first, C, taps, act, (const bf16*)bias};
+  ConvP p{U, ldu, (const bf16*)w, Y, ldy, state, slot_stride, slot, pos, first, C, taps, act, (const bf16*)bias, residual};
   const int by = cdiv(C, 256) < 8 ? cdiv(C, 256) : 8;
   short_conv_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
@@ -727,16 +854,36 @@ int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long l
   return B200_OK;
 }
 
+int b200_lm_token_shift(const float* h, long ldh, const void* mu, float* M, long ldm, long mix_stride, float* state,
+                        long slot_stride, const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C,
+                        int n_mix, int single, int T, void* st) {
+  B200_REQUIRE(h && mu && M && state && slot && pos && first && seqs && T > 0 && n_seq > 0 && C > 0 && n_mix > 0,
+               "lm_token_shift: bad argument");
+  ShiftP p{h, ldh, (const bf16*)mu, M, ldm, mix_stride, state, slot_stride, slot, pos, first, C, n_mix, single};
+  const int by = cdiv(C, 256) < 8 ? cdiv(C, 256) : 8;
+  token_shift_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(p);
+  B200_CHECK_LAUNCH();
+  if (!single) {
+    token_shift_state_kernel<<<dim3(n_seq, by), 256, 0, (cudaStream_t)st>>>(p, seqs);
+    B200_CHECK_LAUNCH();
+  }
+  return B200_OK;
+}
+
 int b200_lm_qkv_post(float* Q, long ldq, const float* K, long ldk, const float* V, long ldv, void* cache, int cache_bf16,
                      long slot_stride, long tok_stride, const int* slot, const int* pos, const float* cs, int H, int G,
-                     int dim, int vdim, int rot_dims, int T, void* st) {
+                     int dim, int vdim, int rot_dims, const void* qn_w, const void* kn_w, float eps, int v_unit, float qt_coef,
+                     int qt_every, const void* vmix, const float* v_first, long ldvf, float* v_keep, long ldvk, int T, void* st) {
   B200_REQUIRE(Q && K && V && cache && slot && pos && T > 0 && H > 0 && G > 0, "lm_qkv_post: bad argument");
+  B200_REQUIRE(!vmix || v_first, "lm_qkv_post: value mixing needs the first layer's values");
   B200_REQUIRE(rot_dims % 2 == 0 && rot_dims <= dim && (rot_dims == 0 || cs), "lm_qkv_post: rotated dims %d of %d", rot_dims, dim);
   if (cache_bf16) {
-    QkvPostP<bf16> p{Q, ldq, K, ldk, V, ldv, (bf16*)cache, slot_stride, tok_stride, slot, pos, (const float2*)cs, H, G, dim, vdim, rot_dims};
+    QkvPostP<bf16> p{Q, ldq, K, ldk, V, ldv, (bf16*)cache, slot_stride, tok_stride, slot, pos, (const float2*)cs, H, G, dim, vdim, rot_dims,
+                      (const bf16*)qn_w, (const bf16*)kn_w, eps, v_unit, qt_coef, qt_every, (const bf16*)vmix, v_first, ldvf, v_keep, ldvk};
     qkv_post_kernel<bf16><<<T, 256, 0, (cudaStream_t)st>>>(p);
   } else {
-    QkvPostP<float> p{Q, ldq, K, ldk, V, ldv, (float*)cache, slot_stride, tok_stride, slot, pos, (const float2*)cs, H, G, dim, vdim, rot_dims};
+    QkvPostP<float> p{Q, ldq, K, ldk, V, ldv, (float*)cache, slot_stride, tok_stride, slot, pos, (const float2*)cs, H, G, dim, vdim, rot_dims,
+                       (const bf16*)qn_w, (const bf16*)kn_w, eps, v_unit, qt_coef, qt_every, (const bf16*)vmix, v_first, ldvf, v_keep, ldvk};
     qkv_post_kernel<float><<<T, 256, 0, (cudaStream_t)st>>>(p);
   }
   B200_CHECK_LAUNCH();
@@ -745,10 +892,11 @@ int b200_lm_qkv_post(float* Q, long ldq, const float* K, long ldk, const float* 
 
 int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cache_bf16, long slot_stride, long tok_stride,
                            const int* slot, const int* pos, float* out, long ldo, const void* sink, int H, int G,
-                           int dim, int vdim, float scale, int chunk, int window, float* part, int n_split, int T,
-                           void* st) {
+                           int dim, int vdim, float scale, int chunk, int window, float bias_exp, int unit_sink, float* part,
+                           int n_split, int T, void* st) {
   B200_REQUIRE(q && cache && slot && pos && out && T > 0 && H > 0 && G > 0 && H % G == 0, "lm_sink_attention: bad argument");
   B200_REQUIRE(vdim <= 256, "lm_sink_attention: value size %d not supported", vdim);
+  B200_REQUIRE(!(sink && unit_sink), "lm_sink_attention: a sink logit per head or the constant one, not both");
   if (n_split < 1 || !part) n_split = 1;
   B200_REQUIRE(n_split <= 64, "lm_sink_attention: at most 64 splits");
   const int rep = H / G, nw = rep < 8 ? rep : 8;
@@ -759,13 +907,13 @@ int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cach
     if (first_use_on_device(&g_sink_attr_bf16))
       B200_CUDA(cudaFuncSetAttribute(sink_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     const int vec = dim % 8 == 0 && vdim % 8 == 0 && tok_stride % 8 == 0 && slot_stride % 8 == 0 && ((uintptr_t)cache & 15) == 0;
-    SinkAttnP<bf16> p{q, ldq, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split, vec};
+    SinkAttnP<bf16> p{q, ldq, (const bf16*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split, vec, bias_exp, unit_sink};
     sink_attention_kernel<bf16><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   } else {
     if (first_use_on_device(&g_sink_attr_f32))
       B200_CUDA(cudaFuncSetAttribute(sink_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     const int vec = dim % 4 == 0 && vdim % 4 == 0 && tok_stride % 4 == 0 && slot_stride % 4 == 0 && ((uintptr_t)cache & 15) == 0;
-    SinkAttnP<float> p{q, ldq, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split, vec};
+    SinkAttnP<float> p{q, ldq, (const float*)cache, slot_stride, tok_stride, slot, pos, out, ldo, (const bf16*)sink, H, G, dim, vdim, scale, chunk, window, part, n_split, vec, bias_exp, unit_sink};
     sink_attention_kernel<float><<<grid, nw * 32, smem, (cudaStream_t)st>>>(p);
   }
   B200_CHECK_LAUNCH();
@@ -781,22 +929,28 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
                          float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
                          int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
                          const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
-                         const float* b, long ldb, int delta, int dt_in, const void* skip, float* prep, int T, void* st) {
+                         const float* b, long ldb, int delta, int dt_in, const void* skip, const float* wraw, long ldwr,
+                         const void* bonus, float* prep, int T, void* st) {
   B200_REQUIRE(q && k && v && out && state && seqs && slot && pos && n_seq > 0 && H > 0 && rep > 0 && H % rep == 0,
                "lm_linear_state: bad argument");
   B200_REQUIRE(dim > 0 && dim <= 32 * LS_R && vdim > 0, "lm_linear_state: key size %d not supported (at most %d)", dim, 32 * LS_R);
-  B200_REQUIRE(decay_const || (a && A_log && dt_bias), "lm_linear_state: a decay per head, or the inputs of a computed one");
+  const bool chan = wraw != nullptr;
+  B200_REQUIRE(chan || decay_const || (a && A_log && dt_bias), "lm_linear_state: a decay per head, or the inputs of a computed one");
+  B200_REQUIRE(!chan || (bonus && prep && rep == 1 && !delta && !dt_in && !act && unit_eps == 0.f && !skip && !decay_const),
+               "lm_linear_state: a decay per key channel comes with a bonus, prepared inputs and nothing else");
   B200_REQUIRE(!dt_in || (!decay_const && !delta && !b), "lm_linear_state: the step size scales the input only in the plain form with a computed decay");
   StateP p{q, ldq, k, ldk, v, ldv, out, ldo, state, slot_stride, seqs, slot, pos, H, rep, dim, vdim, act, unit_eps, q_scale,
-           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta, dt_in, (const bf16*)skip};
+           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta, dt_in, (const bf16*)skip, nullptr, 0};
   const cudaStream_t cs = (cudaStream_t)st;
   if (prep) {     // scratch of T * (2 Hk dim + Hk + 2 H) floats: the per-token work runs first, over all tokens at once
     B200_REQUIRE(T > 0, "lm_linear_state: the prepared path needs the number of tokens");
     const int Hk = H / rep;
     const long n = (long)Hk * dim;
+    // scratch: the same T * (2 Hk dim + Hk + 2 H) floats, or, with a decay per channel, T * (3 H dim + H)
     float *qn = prep, *kn = qn + (long)T * n, *kq = kn + (long)T * n, *dec = kq + (long)T * Hk, *bet = dec + (long)T * H;
     StatePrepP pp{q, ldq, k, ldk, qn, kn, n, kq, dec, bet, H, Hk, dim, act, unit_eps, q_scale, decay_const, a, lda,
-                  (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, dt_in};
+                  (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, dt_in, wraw, ldwr, chan ? dec : nullptr, (const bf16*)bonus};
+    if (chan) { p.wdec = dec; p.ldw = n; }
     state_prep_kernel<<<T, 128, 0, cs>>>(pp);
     B200_CHECK_LAUNCH();
     p.q = qn; p.ldq = n; p.k = kn; p.ldk = n; p.kq_in = kq; p.dec_in = dec; p.bet_in = bet;
@@ -805,8 +959,9 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
 #define LS_LAUNCH(PP)                                                                                            \
   do {                                                                                                           \
     const dim3 grid(n_seq, H, cdiv(vdim, LS_THREADS / PP));                                                      \
-    if (delta) linear_state_kernel<PP, true><<<grid, block, 0, cs>>>(p);                                         \
-    else linear_state_kernel<PP, false><<<grid, block, 0, cs>>>(p);                                              \
+    if (chan) linear_state_kernel<PP, false, true><<<grid, block, 0, cs>>>(p);                                   \
+    else if (delta) linear_state_kernel<PP, true, false><<<grid, block, 0, cs>>>(p);                             \
+    else linear_state_kernel<PP, false, false><<<grid, block, 0, cs>>>(p);                                       \
   } while (0)
   if (dim <= LS_R) LS_LAUNCH(1);
   else if (dim <= 2 * LS_R) LS_LAUNCH(2);
@@ -827,10 +982,11 @@ int b200_lm_heads_to_bf16(const float* q, long ldq, int rep, int dim, void* out,
 }
 
 int b200_lm_sink_softmax_bf16(const float* S, long lds, const int* pos, int rep, const void* sink, float scale, int chunk,
-                              int window, int key0, void* P, long ldp, int rows, int Sp, void* st) {
+                              int window, int key0, float bias_exp, int head0, int H, int unit_sink, void* P, long ldp,
+                              int rows, int Sp, void* st) {
   B200_REQUIRE(S && pos && P && rows > 0 && rep > 0 && Sp > 0 && key0 >= 0, "lm_sink_softmax_bf16: bad argument");
   sink_softmax_bf16_kernel<<<rows, 256, 0, (cudaStream_t)st>>>(S, lds, pos, rep, (const bf16*)sink, scale, chunk, window,
-                                                                key0, (bf16*)P, ldp, Sp);
+                                                                key0, bias_exp, head0, H > 0 ? H : 1, unit_sink, (bf16*)P, ldp, Sp);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
@@ -849,24 +1005,24 @@ int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, con
   return B200_OK;
 }
 
-int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
+int b200_lm_glu_clamp(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float cubic, float up_off,
                       float* Y, long ldy, int n, int T, void* st) {
   B200_REQUIRE(G && U && Y && T > 0 && n > 0, "lm_glu_clamp: bad argument");
   const bool v4 = n % 4 == 0 && ldg % 4 == 0 && ldu % 4 == 0 && ldy % 4 == 0 &&
                   (((uintptr_t)G | (uintptr_t)U | (uintptr_t)Y) & 15) == 0;
-  if (v4 && T > 16) glu_clamp4_kernel<<<dim3(T, cdiv(n, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, Y, ldy, n);
-  else glu_clamp_kernel<<<dim3(T, cdiv(n, 256)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, Y, ldy, n);
+  if (v4 && T > 16) glu_clamp4_kernel<<<dim3(T, cdiv(n, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, cubic, up_off, Y, ldy, n);
+  else glu_clamp_kernel<<<dim3(T, cdiv(n, 256)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, cubic, up_off, Y, ldy, n);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }
 
-int b200_lm_glu_clamp_bf16(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float up_off,
+int b200_lm_glu_clamp_bf16(const float* G, long ldg, const float* U, long ldu, float limit, float alpha, float cubic, float up_off,
                            void* Y, int n, int Kp, const int* live, int T, void* st) {
   B200_REQUIRE(G && U && Y && T > 0 && n > 0 && Kp >= n, "lm_glu_clamp_bf16: bad argument");
   const bool v4 = n % 4 == 0 && Kp % 4 == 0 && ldg % 4 == 0 && ldu % 4 == 0 && (((uintptr_t)G | (uintptr_t)U) & 15) == 0 &&
                   ((uintptr_t)Y & 7) == 0;
-  if (v4) glu_clamp_bf16x4_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp, live);
-  else glu_clamp_bf16_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, up_off, (bf16*)Y, n, Kp, live);
+  if (v4) glu_clamp_bf16x4_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, cubic, up_off, (bf16*)Y, n, Kp, live);
+  else glu_clamp_bf16_kernel<<<dim3(T, cdiv(Kp, 1024)), 256, 0, (cudaStream_t)st>>>(G, ldg, U, ldu, limit, alpha, cubic, up_off, (bf16*)Y, n, Kp, live);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

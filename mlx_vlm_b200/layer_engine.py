@@ -111,7 +111,7 @@ class LayerEngine:
         n = x.shape[0] if want is None else want.shape[0]
         xn = ops.empty((n, c.width))
         ops.norm_rows(x, c.final_norm, c.eps, xn, w_offset=getattr(c, "norm_offset", 1.0), rows=want,
-                      center=getattr(c, "norm_center", False))
+                      center=getattr(c, "norm_center", False), groups=getattr(c, "norm_groups", 1))
         cap, mul = c.logit_softcap, float(getattr(c, "logit_scale", 1.0))
         if not cap and mul != 1.0:        # a design whose logits are the head's product times a constant
             return ops.linear(xn, c.head, epi=EPI_SCALE, epi_param=mul)

@@ -25,6 +25,21 @@ and, for pre-norm layers with a layer norm before each sublayer and a scale vect
                                                        expert with a gate per token)
   layer          ScaledPreNormLayer: x += s1 * mixer(LN(x)); x += s2 * ff(LN(x))
 
+and, for pre-norm layers with an RMS norm in groups, ONE multiplier on both branches and a causal convolution over time
+on what the mixer reads:
+
+  mixers         CONV_MIXERS["attention"]    -> GroupedAttention with norms over the whole query / key projection,
+                                                 YaRN-scaled rotate-half rotary, unit-length values, a sink logit per head
+                 CONV_MIXERS["attention_2"]  -> GroupedAttention without rotation: a query temperature that grows with the
+                                                 position, a distance bias per head, a sliding window, one in the denominator
+                 (both: values mixed with those of the first such layer)
+                 CONV_MIXERS["wkv"]          -> TokenShiftState (token shift, a decay per key channel made from the input,
+                                                 a bonus for the current token, a matrix state per head)
+  feed-forwards  CONV_FEEDFORWARDS["dense"]  -> GatedDense with the tanh form of gelu on the gate
+                 CONV_FEEDFORWARDS["moe"]    -> UngatedExpertMixture (softmax scores, the choice limited to the best groups,
+                                                 erf-gelu experts, a shared expert)
+  layer          ConvPreNormLayer: h = N1(x); h += conv(h); x += m * mixer(h); x += m * ff(N2(x))
+
 A block declares `manifest(prefix)` (packed name, shape) and `pack(prefix, checkpoint tensors, arena)`; the model
 packs all blocks into ONE device arena (the layout the other models of this package use).  `forward(ctx, x)`
 enqueues the block's kernels; `ctx` carries the per-token slot / position arrays of the step and the cache pool,
@@ -38,7 +53,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .._native import B200Error as _B200Error
-from .layer_ops import EPI_RELU2, LayerOps
+from .layer_ops import ACT_GELU, EPI_GELU, EPI_RELU2, EPI_SOFTCAP, GELU_TANH_ALPHA, GELU_TANH_CUBIC, LayerOps
 
 
 @dataclass
@@ -51,6 +66,7 @@ class StepCtx:
     segments: Optional[List] = None   # host view of the step: (first token, tokens, slot, first position) per request
     _rope: Dict = field(default_factory=dict)
     _seq: Optional[tuple] = None
+    carry: Dict = field(default_factory=dict)     # what one layer of the step leaves for later ones (rows of the step)
 
     def seq_tables(self):
         """(first (T,), seqs (G, 2), G): the sequences of the step for the mixers that walk them in order; without a
@@ -785,12 +801,18 @@ class StateSpaceMixer:
 class GatedDense:
     """Gated feed-forward W_down (g sigmoid(alpha g) (u + offset)), g = min(W_gate n, limit), u = clamp(W_up n, +-limit);
     without a limit, alpha = 1 and offset = 0 it is the silu-gated unit W_down (silu(W_gate n) * W_up n).  Gate and up
-    are one stacked product."""
+    are one stacked product.  act = "gelu_tanh": the gate passes the tanh form of gelu instead,
+    g sigmoid(2 sqrt(2 / pi) (g + 0.044715 g^3)) = 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))."""
 
-    def __init__(self, index: int, cfg: dict, width: int, clamped: bool = False, alpha: float = 1.702):
+    def __init__(self, index: int, cfg: dict, width: int, clamped: bool = False, alpha: float = 1.702, act: str = "silu"):
         self.index, self.W, self.ff = index, width, int(cfg["ff"])
         self.limit = float(cfg["limit"]) if clamped else float("inf")
         self.alpha, self.offset = (alpha, 1.0) if clamped else (1.0, 0.0)
+        if act not in ("silu", "gelu_tanh"):
+            raise ValueError(f"layer {index}: activation {act!r} (have 'silu', 'gelu_tanh')")
+        self.cubic = 0.0
+        if act == "gelu_tanh":
+            self.alpha, self.cubic = GELU_TANH_ALPHA, GELU_TANH_CUBIC
         self.w: Dict[str, torch.Tensor] = {}
 
     def manifest(self, p: str):
@@ -815,14 +837,15 @@ class GatedDense:
         down = self.w["down"]
         if ops.tc_ok(x.shape[0], self.ff, down.stride(0)) and down.data_ptr() % 16 == 0:
             try:          # a prompt: the activation is written as the bf16 operand of the down product, in one pass
-                hb = ops.glu_clamp_bf16(D[:, :self.ff], D[:, self.ff:], self.limit, self.alpha, up_offset=self.offset)
+                hb = ops.glu_clamp_bf16(D[:, :self.ff], D[:, self.ff:], self.limit, self.alpha, up_offset=self.offset,
+                                        cubic=self.cubic)
                 y = ops.empty((x.shape[0], self.W))
                 ops.tc_gemm(hb, down, y, N_=self.W, K=self.ff, ldw=down.stride(0))
                 return y
             except _B200Error as e:
                 ops.tc_refused(e)
         hid = ops.empty((x.shape[0], self.ff))
-        ops.glu_clamp(D[:, :self.ff], D[:, self.ff:], self.limit, self.alpha, hid, up_offset=self.offset)
+        ops.glu_clamp(D[:, :self.ff], D[:, self.ff:], self.limit, self.alpha, hid, up_offset=self.offset, cubic=self.cubic)
         return ops.linear(hid, down)
 
     def forward(self, ctx: StepCtx, x: torch.Tensor) -> dict:
@@ -996,6 +1019,451 @@ class ScaledPreNormLayer:
             return None
         n = ctx.ops.empty(tuple(x.shape))
         ctx.ops.residual_norm_rows(x=x, ls=ls, w=norm_w, eps=ctx.eps, out=n, center=True, **branch)
+        return n
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Pre-norm layers with an RMS norm in groups, one multiplier on both branches and a causal convolution on the mixer's
+# input.  A mixer has `forward(ctx, h) -> rows (T, width)`, `kv_dim` / `cache_index` and `state_floats` / `state_off` like
+# the mixers of a ScaledPreNormLayer; a feed-forward has `forward(ctx, n) -> keyword arguments of ops.residual_rows`.
+class GroupedAttention:
+    """Softmax attention with `heads` query heads over `kv_heads` key/value heads (query head h reads key/value head
+    h // (heads / kv_heads)), q, k, v one stacked product of the mixer's input.  Optional, each by a parameter:
+      qk_norm     q and k are RMS-normed over their WHOLE projection (all heads at once) and weighted (`q.norm`, `k.norm`)
+      rot         rotate-half rotary on the first `rot.dims` numbers of every head, YaRN-scaled by `rot.scaling`
+      v_unit      every value head is divided by its root mean square; the cache holds it so
+      sink        "learned": a logit per head (`sink`) joins the softmax's denominator without a key or a value;
+                  "unit": the denominator holds one more 1 (a sink logit of zero)
+      q_temp      queries times 1 + coef ln(floor((p + 1) / every) + 1) at position p
+      bias_exp    slope_h (i - j) is taken off the score of query i and key j, slope_h = 2^(-bias_exp (h + 1) / heads)
+      mask.size   query i sees the keys j with 0 <= i - j < size (absent: every j <= i)
+      v_mix       the model marks the first mixing layer (`v_role = "first"`: its cached values are also kept for the
+                  step) and the later ones (`"blend"`: v <- (1 - lam) v + lam v_first, lam = `vmix`, after the value norm)."""
+
+    def __init__(self, index: int, cfg: dict, width: int, qk_norm: bool = False, v_unit: bool = False,
+                 sink: Optional[str] = None, bias_exp: float = 0.0):
+        self.index, self.W = index, width
+        self.H, self.dim = int(cfg["heads"]), int(cfg["dim"])
+        self.G, self.vdim = int(cfg.get("kv_heads", self.H)), int(cfg.get("vdim", self.dim))
+        if self.H % self.G:
+            raise ValueError(f"layer {index}: {self.H} query heads do not divide over {self.G} key/value heads")
+        self.scale = float(cfg.get("scale", float(self.dim) ** -0.5))
+        rot = cfg.get("rot") or {}
+        self.rot_base, self.rot_dims = float(rot.get("base", 10000.0)), int(rot.get("dims", 0))
+        sc = rot.get("scaling")
+        self.rot_scaling = None if not sc else (float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"]))
+        if self.rot_dims % 2 or self.rot_dims > self.dim:
+            raise ValueError(f"layer {index}: {self.rot_dims} rotated numbers in heads of {self.dim}")
+        self.window = int((cfg.get("mask") or {}).get("size", 0))
+        qt = cfg.get("q_temp")
+        self.q_temp = None if not qt else (float(qt["coef"]), int(qt["every"]))
+        if sink not in (None, "learned", "unit"):
+            raise ValueError(f"layer {index}: sink {sink!r} (have None, 'learned', 'unit')")
+        self.qk_norm, self.v_unit, self.sink, self.bias_exp = bool(qk_norm), bool(v_unit), sink, float(bias_exp)
+        self.v_mix = bool(cfg.get("v_mix"))
+        self.v_role: Optional[str] = None      # set by the model: "first" / "blend"
+        self.n_q, self.n_k, self.n_v = self.H * self.dim, self.G * self.dim, self.G * self.vdim
+        self.kv_dim, self.state_floats = self.n_k + self.n_v, 0
+        self.cache_index, self.state_off = -1, 0
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def manifest(self, p: str):
+        out = [(p + "qkv", (self.n_q + self.n_k + self.n_v, self.W)), (p + "o", (self.W, self.H * self.vdim))]
+        if self.qk_norm:
+            out += [(p + "q.norm", (self.n_q,)), (p + "k.norm", (self.n_k,))]
+        if self.sink == "learned":
+            out.append((p + "sink", (self.H,)))
+        if self.v_mix:
+            out.append((p + "vmix", (1,)))
+        return out
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        out = {p + "q": (self.n_q, self.W), p + "k": (self.n_k, self.W), p + "v": (self.n_v, self.W),
+               p + "o": (self.W, self.H * self.vdim)}
+        if self.qk_norm:
+            out.update({p + "q.norm": (self.n_q,), p + "k.norm": (self.n_k,)})
+        if self.sink == "learned":
+            out[p + "sink"] = (self.H,)
+        if self.v_mix:
+            out[p + "vmix"] = ()
+        return out
+
+    def pack(self, p: str, ck, view):
+        qkv = view(p + "qkv")
+        qkv[:self.n_q].copy_(ck[p + "q"])
+        qkv[self.n_q:self.n_q + self.n_k].copy_(ck[p + "k"])
+        qkv[self.n_q + self.n_k:].copy_(ck[p + "v"])
+        for n, shape in self.manifest(p)[1:]:
+            view(n).copy_(ck[n].reshape(shape))
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n[len(p):]: view(n) for n, _ in self.manifest(p)}
+
+    def forward(self, ctx: StepCtx, h: torch.Tensor) -> torch.Tensor:
+        ops, w, T = ctx.ops, self.w, h.shape[0]
+        nq, nk, nv = self.n_q, self.n_k, self.n_v
+        D = ops.linear(h, w["qkv"])
+        q, k, v = D[:, :nq], D[:, nq:nq + nk], D[:, nq + nk:]
+        rows = ctx.pool.buf[self.cache_index][..., :self.kv_dim]
+        v_first = keep = None
+        if self.v_role == "first":
+            keep = ctx.carry["v_first"] = ops.empty((T, nv))
+        elif self.v_role == "blend":
+            v_first = ctx.carry["v_first"]
+        ops.qkv_post(q, k, v, rows, ctx.slot, ctx.pos, ctx.rope(self.rot_base, self.rot_dims, self.rot_scaling), self.H, self.G,
+                     self.dim, self.vdim, self.rot_dims, q_norm=w.get("q.norm"), k_norm=w.get("k.norm"), eps=ctx.eps,
+                     v_unit=self.v_unit, q_temp=self.q_temp, vmix=w["vmix"] if v_first is not None else None,
+                     v_first=v_first, v_keep=keep)
+        o = ops.empty((T, self.H * self.vdim))
+        segs = ctx.segments or []
+        done = False
+        if rows.dtype == torch.bfloat16 and any(self._tc_portion(ops, n, rows) for _, n, _, _ in segs):
+            try:
+                for start, n, slot, p0 in segs:      # long portions on the tensor cores, the rest on the row kernel
+                    sl = slice(start, start + n)
+                    if self._tc_portion(ops, n, rows):
+                        self._attend_prompt(ctx, q[sl], rows, slot, ctx.pos[sl], o[sl], p0, n)
+                    else:
+                        self._attend_rows(ctx, q[sl], rows, ctx.slot[sl], ctx.pos[sl], o[sl], prompt=True)
+                done = True
+            except _B200Error as e:
+                ops.tc_refused(e)
+        if not done:
+            self._attend_rows(ctx, q, rows, ctx.slot, ctx.pos, o, prompt=ctx.segments is not None)
+        return ops.linear(o, w["o"])
+
+    def _tc_portion(self, ops: LayerOps, n: int, rows) -> bool:
+        return ops.tc_ok(n, self.dim, rows.stride(1)) and rows.stride(0) % 8 == 0
+
+    def _attend_rows(self, ctx: StepCtx, q, rows, slot, pos, o, prompt: bool):
+        """the row kernel: every query finds its keys by (slot, position); a step of few tokens (decoding) spreads the
+        keys of a query over several blocks"""
+        ctx.ops.sink_attention(q, rows, slot, pos, o, self.w.get("sink"), self.H, self.G, self.dim, self.vdim, self.scale,
+                               window=self.window, n_split=1 if prompt and q.shape[0] > 16 else None,
+                               bias_exp=self.bias_exp, unit_sink=self.sink == "unit")
+
+    def _attend_prompt(self, ctx: StepCtx, q, all_rows, slot_index: int, pos, o, p0: int, n: int):
+        """A portion of a prompt (positions p0 .. p0 + n - 1 of one slot) as two tcgen05 products per key/value head:
+        the head's cached key columns are the weight-major operand of the scores of the query heads that share it, an
+        fp32 softmax over the visible keys (distance bias and sink included) writes bf16 probabilities, and the head's
+        value columns, transposed, are the operand of the weighted sum.  Queries are taken in chunks that bound the
+        score buffer; with a window a chunk is about a window long and meets only the keys from its first query's
+        first visible key on."""
+        ops, H, G, d, dv = ctx.ops, self.H, self.G, self.dim, self.vdim
+        rep, rows = H // G, all_rows[slot_index]
+        sink = self.w.get("sink")
+        step = n
+        if self.window:
+            step = max(128, min(self.window, (1 << 27) // (rep * 2 * self.window)))
+            step = -(-n // -(-n // step))          # equal chunks: no short one at the end
+        for a in range(0, n, step):
+            m = min(step, n - a)
+            key0 = max(p0 + a - self.window + 1, 0) if self.window else 0
+            S = p0 + a + m - key0
+            Sp = (S + 63) // 64 * 64
+            sub = max(1, min(m, (1 << 27) // (rep * Sp)))
+            for g in range(G):
+                keys = rows[key0:key0 + S, g * d:(g + 1) * d]
+                vt = ops.cache_transpose(rows[key0:, G * d + g * dv:], S, Sp, dv)
+                for b in range(a, a + m, sub):
+                    mm = min(sub, a + m - b)
+                    qb16 = ops.heads_to_bf16(q[b:b + mm, g * rep * d:], rep, d)
+                    sc = ops.empty((mm * rep, S))
+                    ops.tc_gemm(qb16, keys, sc, N_=S, K=d, ldw=rows.stride(0))
+                    P = ops.empty((mm * rep, Sp), torch.bfloat16)
+                    ops.sink_softmax_bf16(sc, pos[b:b + mm], rep, None if sink is None else sink[g * rep:], self.scale, 0,
+                                          self.window, key0, P, bias_exp=self.bias_exp, head0=g * rep, H=H,
+                                          unit_sink=self.sink == "unit")
+                    og = ops.empty((mm * rep, dv))
+                    ops.tc_gemm(P, vt, og, N_=dv, K=Sp)
+                    ops.head_post(og.view(mm, rep * dv), o[b:b + mm, g * rep * dv:(g + 1) * rep * dv], dv=dv)
+
+
+class TokenShiftState:
+    """Time mixing with a token shift and a matrix state per head (the RWKV family's form).  With h' the input of the
+    token before (zeros for a sequence's first token; the slot keeps the last one), each of r, k, v, g, w reads its own
+    mix h + (h' - h) mu_s.  r, k, v = W_r, W_k, W_v of their mixes (`heads` x `dim`), gate = silu(W_g mix_g), and the
+    decay per head and key channel  w = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0)).  Per head, with S (dim, dim) fp32 in the slot,
+    zero at position 0:  o = (S + diag(u) k v^T)^T r  (the bonus u counts for the current token only),  then
+    S <- diag(w) S + k v^T.  Every head's o is divided by its root mean square, the heads side by side are multiplied by
+    `norm` and the gate, then W_o."""
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, index: int, cfg: dict, width: int):
+        self.index, self.W = index, width
+        self.H, self.dim = int(cfg["heads"]), int(cfg["dim"])
+        self.n = self.H * self.dim
+        self.rank = int(cfg.get("decay_rank", 0))      # 0: taken from the checkpoint's `w1` when the weights are packed
+        self.kv_dim = 0
+        self.cache_index, self.state_off = -1, 0
+        self.w: Dict[str, torch.Tensor] = {}
+
+    @property
+    def state_floats(self) -> int:
+        return self.W + state_floats(self.H, self.dim, self.dim)
+
+    def set_rank(self, rank: int):
+        self.rank = int(rank)
+
+    def manifest(self, p: str):
+        return [(p + "mu", (len(self.MIXES), self.W)), (p + "rkvg", (4, self.n, self.W)), (p + "w1", (self.rank, self.W)),
+                (p + "w2", (self.n, self.rank)), (p + "w0", (self.n,)), (p + "u", (self.H, self.dim)), (p + "norm", (self.n,)),
+                (p + "o", (self.W, self.n))]
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        out = {p + "mu." + s: (self.W,) for s in self.MIXES}
+        out.update({p + s: (self.n, self.W) for s in "rkvg"})
+        out.update({p + "w1": (self.rank, self.W), p + "w2": (self.n, self.rank), p + "w0": (self.n,),
+                    p + "u": (self.H, self.dim), p + "norm": (self.n,), p + "o": (self.W, self.n)})
+        return out
+
+    def pack(self, p: str, ck, view):
+        mu, rkvg = view(p + "mu"), view(p + "rkvg")
+        for i, s in enumerate(self.MIXES):
+            mu[i].copy_(ck[p + "mu." + s])
+        for i, s in enumerate("rkvg"):
+            rkvg[i].copy_(ck[p + s])
+        for n in ("w1", "w2", "w0", "u", "norm", "o"):
+            view(p + n).copy_(ck[p + n])
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n[len(p):]: view(n) for n, _ in self.manifest(p)}
+
+    def forward(self, ctx: StepCtx, h: torch.Tensor) -> torch.Tensor:
+        ops, w, T, n, W = ctx.ops, self.w, h.shape[0], self.n, self.W
+        st, off = ctx.pool.state, self.state_off
+        M = ops.token_shift(h, w["mu"], st[:, off:off + W], ctx)          # (5, T, W)
+        D = ops.empty((T, 4 * n))                                          # r | k | v | gate
+        if ops.tc_ok(T, W):           # a prompt: four tensor-core products
+            for i in range(4):
+                ops.linear(M[i], w["rkvg"][i], out=D[:, i * n:(i + 1) * n])
+        else:                         # few rows: ONE launch over the four (input, weight) pairs
+            ops.gemm(M, w["rkvg"], D, M=T, N_=n, K=W, ldx=W, xb=T * W, wb=n * W, ldy=4 * n, yb=n, batch=4)
+        lat = ops.linear(M[4], w["w1"], epi=EPI_SOFTCAP, epi_param=1.0)    # tanh
+        logit = ops.linear(lat, w["w2"], bias=w["w0"])
+        o = ops.empty((T, n))
+        ops.linear_state(D[:, :n], D[:, n:2 * n], D[:, 2 * n:3 * n], o, st[:, off + W:off + self.state_floats], ctx, H=self.H,
+                         rep=1, dim=self.dim, vdim=self.dim, decay_logits=logit, bonus=w["u"])
+        ops.head_post(o, o, dv=self.dim, gate=D[:, 3 * n:], gate_silu=True, w=w["norm"], eps=ctx.eps, span=self.dim)
+        return ops.linear(o, w["o"])
+
+
+class UngatedDense:
+    """W_down act(W_up n), act = the exact (erf) gelu."""
+
+    def __init__(self, index: int, cfg: dict, width: int):
+        self.index, self.W, self.ff = index, width, int(cfg["ff"])
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def manifest(self, p: str):
+        return [(p + "up", (self.ff, self.W)), (p + "down", (self.W, self.ff))]
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        return dict(self.manifest(p))
+
+    def pack(self, p: str, ck, view):
+        for n, _ in self.manifest(p):
+            view(n).copy_(ck[n])
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n[len(p):]: view(n) for n, _ in self.manifest(p)}
+
+    def rows(self, ctx: StepCtx, x: torch.Tensor) -> torch.Tensor:
+        ops, up, down = ctx.ops, self.w["up"], self.w["down"]
+        if ops.tc_ok(x.shape[0], self.W, self.ff):
+            try:          # a prompt: the activation is written as the bf16 operand of the down product, in one pass
+                hid = ops.linear(x, up)
+                y = ops.empty((x.shape[0], self.W))
+                ops.tc_gemm(ops.to_bf16(hid, self.ff, act=ACT_GELU), down, y, N_=self.W, K=self.ff)
+                return y
+            except _B200Error as e:
+                ops.tc_refused(e)
+        return ops.linear(ops.linear(x, up, epi=EPI_GELU), down)
+
+    def forward(self, ctx: StepCtx, x: torch.Tensor) -> dict:
+        return {"y": self.rows(ctx, x)}
+
+
+class UngatedExpertMixture:
+    """`experts` ungated feed-forwards W_down gelu(W_up n) (exact gelu, no biases) of which a token uses `top`.  Scores
+    s = softmax(W_router n) over all experts, in fp32; the experts form `groups.count` equal groups of neighbours, a
+    group's score is its largest s, and only experts of the `groups.keep` best groups can be chosen; the `top` largest s
+    among them are chosen and weighted by s over the sum of the chosen s (+ 1e-20).  `shared`: one more such
+    feed-forward that every token uses, added with weight one."""
+
+    def __init__(self, index: int, cfg: dict, width: int):
+        self.index, self.W = index, width
+        r = cfg["router"]
+        self.E, self.top, self.ff = int(r["experts"]), int(r["top"]), int(cfg["expert"]["ff"])
+        g = r.get("groups") or {}
+        self.n_groups, self.keep = int(g.get("count", 1)), int(g.get("keep", g.get("count", 1)))
+        if self.E % self.n_groups or not 1 <= self.keep <= self.n_groups or self.top > self.keep * (self.E // self.n_groups):
+            raise ValueError(f"layer {index}: {self.E} experts in {self.n_groups} groups, {self.keep} kept, {self.top} chosen")
+        self.shared = UngatedDense(index, cfg["shared"], width) if cfg.get("shared") else None
+        self.w: Dict[str, torch.Tensor] = {}
+
+    def manifest(self, p: str):
+        out = [(p + "router", (self.E, self.W)), (p + "up", (self.E, self.ff, self.W)), (p + "down", (self.E, self.W, self.ff))]
+        return out + (self.shared.manifest(p + "shared.") if self.shared else [])
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        out = {p + "router": (self.E, self.W)}
+        for e in range(self.E):
+            out.update({p + f"e{e}.up": (self.ff, self.W), p + f"e{e}.down": (self.W, self.ff)})
+        if self.shared:
+            out.update(self.shared.checkpoint_tensors(p + "shared."))
+        return out
+
+    def pack(self, p: str, ck, view):
+        view(p + "router").copy_(ck[p + "router"])
+        up, down = view(p + "up"), view(p + "down")
+        for e in range(self.E):
+            up[e].copy_(ck[p + f"e{e}.up"])
+            down[e].copy_(ck[p + f"e{e}.down"])
+        if self.shared:
+            self.shared.pack(p + "shared.", ck, view)
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n: view(p + n) for n in ("router", "up", "down")}
+        if self.shared:
+            self.shared.bind(p + "shared.", view)
+
+    def forward(self, ctx: StepCtx, x: torch.Tensor) -> dict:
+        ops, w, T, ff = ctx.ops, self.w, x.shape[0], self.ff
+        z = ops.linear(x, w["router"], exact_x=True)      # scores decide the choice: fp32 input rows in every mode
+        idx, wgt = ops.router_group_topk(z, self.top, None, self.n_groups, self.keep, E=self.E, softmax=True, group_max=True)
+        lists, count = ops.moe_group(idx, self.E)
+        out = None
+        if ops.tc_ok(T, self.W, ff):
+            try:
+                out = self._experts_prompt(ops, x, lists, count)
+            except _B200Error as e:
+                ops.tc_refused(e)
+        if out is None:
+            n_act = min(self.E, T * self.top)
+            hid = ops.empty((T * self.top, ff))
+            ops.gemm(x, w["up"], hid, M=T, N_=ff, K=self.W, wb=ff * self.W, batch=self.E, lists=lists, count=count,
+                     x_div=self.top, epi=EPI_GELU, compact=n_act)
+            out = ops.empty((T * self.top, self.W))
+            ops.gemm(hid, w["down"], out, M=T, N_=self.W, K=ff, wb=self.W * ff, batch=self.E, lists=lists, count=count,
+                     x_div=1, compact=n_act)
+        res = {"y": out, "combine": wgt, "top": self.top}
+        if self.shared:
+            res["shared"] = self.shared.rows(ctx, x)
+        return res
+
+    def _experts_prompt(self, ops: LayerOps, x, lists, count):
+        """A prompt step on the tensor cores (see ExpertMixture._experts_prompt): entries sorted by expert into
+        segments of whole token tiles, ONE grouped tcgen05 launch per projection, the gelu between them applied while
+        the hidden rows are rounded to the next product's operand."""
+        w, T, ff = self.w, x.shape[0], self.ff
+        n_all = T * self.top
+        order, group = ops.moe_tiles(lists, count, n_all)
+        n_rows = order.shape[0]
+        xs = ops.to_bf16(x, self.W, rows=n_rows, row_map=order, div=self.top)
+        hs = ops.empty((n_rows, ff))
+        ops.tc_gemm_grouped(xs, w["up"], hs, group, N_=ff, K=self.W, n_groups=self.E)
+        hb = ops.to_bf16(hs, ff, act=ACT_GELU)
+        ys = ops.empty((n_rows, self.W))
+        ops.tc_gemm_grouped(hb, w["down"], ys, group, N_=self.W, K=ff, n_groups=self.E)
+        out = ops.empty((n_all, self.W))
+        ops.rows_scatter(ys, order, out, n_rows)
+        return out
+
+
+DISTANCE_BIAS_EXP = 8.0       # 'attention_2': head h of H takes 2^(-8 (h + 1) / H) per position of distance off its scores
+
+CONV_MIXERS = {"attention": lambda i, c, w: GroupedAttention(i, c, w, qk_norm=True, v_unit=True, sink="learned"),
+               "attention_2": lambda i, c, w: GroupedAttention(i, c, w, sink="unit", bias_exp=DISTANCE_BIAS_EXP),
+               "wkv": TokenShiftState}
+CONV_FEEDFORWARDS = {"dense": lambda i, c, w: GatedDense(i, c, w, act="gelu_tanh"), "moe": UngatedExpertMixture}
+
+
+class ConvPreNormLayer:
+    """h = N1(x);  h <- h + conv(h);  x <- x + m * mixer(h);  x <- x + m * ff(N2(x)).
+    N: the row in `groups` equal consecutive parts, each divided by sqrt(mean(part^2) + eps), the whole times w.
+    conv: a causal convolution over time per channel (`canon1`, (width, taps), no bias), conv(h)_t = sum_j c[:, j]
+    h_(t - taps + 1 + j); the slot keeps the last taps - 1 rows of N1(x) of its sequence (taps 0: no convolution).
+    The residual stream and both updates are fp32."""
+
+    def __init__(self, index: int, cfg: dict, width: int, groups: int = 1, mult: float = 1.0, taps: int = 0):
+        self.index, self.W, self.groups, self.mult, self.taps = index, width, int(groups), float(mult), int(taps)
+        if width % self.groups:
+            raise ValueError(f"layer {index}: rows of {width} numbers in {self.groups} norm groups")
+        if cfg["type"] not in CONV_MIXERS:
+            raise ValueError(f"layer {index}: unknown mixer type {cfg['type']!r} (have {sorted(CONV_MIXERS)})")
+        self.mixer = CONV_MIXERS[cfg["type"]](index, cfg["mixer"], width)
+        f = cfg.get("mlp")
+        if f is not None and f.get("kind") not in CONV_FEEDFORWARDS:
+            raise ValueError(f"layer {index}: unknown feed-forward kind {f.get('kind')!r} (have {sorted(CONV_FEEDFORWARDS)})")
+        self.ff = None if f is None else CONV_FEEDFORWARDS[f["kind"]](index, f, width)
+        self.kv_dim = self.mixer.kv_dim
+        self.conv_floats = max(self.taps - 1, 0) * width
+        self.state_off = 0            # set by the model: the layer's span of the slot's state = [conv rows | the mixer's]
+        self.w: Dict[str, torch.Tensor] = {}
+
+    @property
+    def state_floats(self) -> int:
+        return self.conv_floats + self.mixer.state_floats
+
+    def _own(self):
+        return [("norm1", (self.W,))] + ([("canon1", (self.W, self.taps))] if self.taps else []) + \
+               ([("norm2", (self.W,))] if self.ff is not None else [])
+
+    def manifest(self, p: str):
+        out = [(p + n, shape) for n, shape in self._own()] + self.mixer.manifest(p + "mix.")
+        return out + (self.ff.manifest(p + "mlp.") if self.ff is not None else [])
+
+    def checkpoint_tensors(self, p: str) -> Dict[str, tuple]:
+        out = {p + n: shape for n, shape in self._own()}
+        out.update(self.mixer.checkpoint_tensors(p + "mix."))
+        if self.ff is not None:
+            out.update(self.ff.checkpoint_tensors(p + "mlp."))
+        return out
+
+    def pack(self, p: str, ck, view):
+        for n, _ in self._own():
+            view(p + n).copy_(ck[p + n])
+        self.mixer.pack(p + "mix.", ck, view)
+        if self.ff is not None:
+            self.ff.pack(p + "mlp.", ck, view)
+        self.bind(p, view)
+
+    def bind(self, p: str, view):
+        self.w = {n: view(p + n) for n, _ in self._own()}
+        self.mixer.bind(p + "mix.", view)
+        if self.ff is not None:
+            self.ff.bind(p + "mlp.", view)
+
+    def forward(self, ctx: StepCtx, x: torch.Tensor, normed: Optional[torch.Tensor] = None,
+                next_norm: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """normed: N1(x) if the layer before already made it; next_norm: the weight of the norm that follows this layer
+        — then the layer's last residual update also norms the updated rows, and the result is returned"""
+        ops = ctx.ops
+        n = normed
+        if n is None:
+            n = ops.empty(tuple(x.shape))
+            ops.norm_rows(x, self.w["norm1"], ctx.eps, n, groups=self.groups)
+        if self.taps:
+            st = ctx.pool.state[:, self.state_off:self.state_off + self.conv_floats]
+            n = ops.short_conv(n, self.w["canon1"], st, ctx, residual=True)
+        y = self.mixer.forward(ctx, n)
+        if self.ff is None:
+            return self._close(ctx, x, {"y": y}, next_norm)
+        n2 = self._close(ctx, x, {"y": y}, self.w["norm2"])
+        return self._close(ctx, x, self.ff.forward(ctx, n2), next_norm)
+
+    def _close(self, ctx: StepCtx, x, branch: dict, norm_w):
+        """x += m * branch; with a norm weight: also the norm of the updated rows (one launch), returned"""
+        if norm_w is None:
+            ctx.ops.residual_rows(x=x, ls=None, mult=self.mult, **branch)
+            return None
+        n = ctx.ops.empty(tuple(x.shape))
+        ctx.ops.residual_norm_rows(x=x, ls=None, w=norm_w, eps=ctx.eps, out=n, mult=self.mult, groups=self.groups, **branch)
         return n
 
 

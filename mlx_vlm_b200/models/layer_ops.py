@@ -15,7 +15,9 @@ import torch
 
 from .. import _native as N
 
-EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_ADD, EPI_SCALE = 0, 1, 2, 3, 4
+EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_ADD, EPI_SCALE, EPI_GELU = 0, 1, 2, 3, 4, 5
+ACT_NONE, ACT_RELU2, ACT_GELU = 0, 1, 2     # activation codes of `to_bf16` (gelu: the exact, erf form)
+GELU_TANH_ALPHA, GELU_TANH_CUBIC = 1.5957691216057308, 0.044715     # z sigmoid(alpha (z + cubic z^3)) = the tanh form of gelu
 SM_COUNT = 148
 TC_MIN_ROWS = 128     # from this many rows on, a product of the bf16 serving mode runs on the tcgen05 GEMM
 WT_F32 = 3            # gemm_wt output mode: fp32 rows
@@ -120,36 +122,39 @@ class LayerOps:
 
     def norm_rows(self, y: torch.Tensor, w: torch.Tensor, eps: float, x: torch.Tensor, *, w_offset: float = 0.0,
                   add: bool = False, combine: Optional[torch.Tensor] = None, top: int = 0,
-                  rows: Optional[torch.Tensor] = None, center: bool = False):
+                  rows: Optional[torch.Tensor] = None, center: bool = False, groups: int = 1):
         """x (T, N) = or += rmsnorm(y rows) * (w_offset + w); `combine` (T, top): y holds `top` rows per token;
-        center: the mean of the row is taken off first (a layer norm without bias)"""
+        center: the mean of the row is taken off first (a layer norm without bias); groups: the row is that many equal
+        consecutive parts, each divided by its own root mean square"""
         T, n = x.shape
         self._ok(self.lib.b200_lm_norm_rows(y.data_ptr(), y.stride(0), N.ptr(combine), int(top), w.data_ptr(),
                                             float(w_offset), float(eps), x.data_ptr(), x.stride(0), int(add),
-                                            N.ptr(rows), int(center), T, n, self.s), "lm_norm_rows")
+                                            N.ptr(rows), int(center), int(groups), T, n, self.s), "lm_norm_rows")
 
     def residual_rows(self, y: torch.Tensor, x: torch.Tensor, ls: Optional[torch.Tensor] = None, *,
                       combine: Optional[torch.Tensor] = None, top: int = 0, shared: Optional[torch.Tensor] = None,
-                      shared_gate: Optional[torch.Tensor] = None):
-        """x (T, N) += ls * (y row, or the `combine`-weighted sum of `top` rows of y per token, + sigmoid(shared_gate)
-        * shared row): the residual update of a branch with a scale vector"""
+                      shared_gate: Optional[torch.Tensor] = None, mult: float = 1.0):
+        """x (T, N) += ls * mult * (y row, or the `combine`-weighted sum of `top` rows of y per token, + sigmoid(shared_gate)
+        * shared row; without a gate the shared row counts fully): the residual update of a branch with a scale vector
+        `ls` and / or a scale number `mult`"""
         T, n = x.shape
         self._ok(self.lib.b200_lm_residual_rows(y.data_ptr(), y.stride(0), N.ptr(combine), int(top), N.ptr(shared),
                                                 shared.stride(0) if shared is not None else 0, N.ptr(shared_gate),
                                                 shared_gate.stride(0) if shared_gate is not None else 0, N.ptr(ls),
-                                                x.data_ptr(), x.stride(0), T, n, self.s), "lm_residual_rows")
+                                                float(mult), x.data_ptr(), x.stride(0), T, n, self.s), "lm_residual_rows")
 
     def residual_norm_rows(self, y: torch.Tensor, x: torch.Tensor, ls: Optional[torch.Tensor], w: torch.Tensor, eps: float,
                            out: torch.Tensor, *, center: bool = False, w_offset: float = 0.0,
                            combine: Optional[torch.Tensor] = None, top: int = 0, shared: Optional[torch.Tensor] = None,
-                           shared_gate: Optional[torch.Tensor] = None):
+                           shared_gate: Optional[torch.Tensor] = None, mult: float = 1.0, groups: int = 1):
         """the update of `residual_rows` on x and, in the same launch, out = norm(updated x) * (w_offset + w): the
         branch's end and the next sublayer's norm read and write the row once"""
         T, n = x.shape
         self._ok(self.lib.b200_lm_residual_norm_rows(
             y.data_ptr(), y.stride(0), N.ptr(combine), int(top), N.ptr(shared), shared.stride(0) if shared is not None else 0,
             N.ptr(shared_gate), shared_gate.stride(0) if shared_gate is not None else 0, N.ptr(ls), x.data_ptr(), x.stride(0),
-            w.data_ptr(), float(w_offset), float(eps), int(center), out.data_ptr(), out.stride(0), T, n, self.s),
+            w.data_ptr(), float(w_offset), float(eps), int(center), out.data_ptr(), out.stride(0), int(groups), float(mult),
+            T, n, self.s),
             "lm_residual_norm_rows")
 
     def latent_post(self, D, wq, wkv, eps, cq, cache_layer, slot, pos, cs, q_rank, kv_rank, rot_dim, rot_dims,
@@ -192,14 +197,17 @@ class LayerOps:
                                               self.s), "lm_router_topk")
         return idx, wgt
 
-    def router_group_topk(self, z, top, correction=None, n_groups: int = 1, keep: int = 1, E: Optional[int] = None):
-        """sigmoid scores; choice on score + correction among the experts of the `keep` best of `n_groups` groups;
+    def router_group_topk(self, z, top, correction=None, n_groups: int = 1, keep: int = 1, E: Optional[int] = None,
+                          softmax: bool = False, group_max: bool = False):
+        """sigmoid scores (softmax: softmax over all experts); choice on score + correction among the experts of the
+        `keep` best of `n_groups` groups (a group's score: the sum of its two largest, or, group_max, its largest);
         weights = the chosen scores over their sum.  z may hold more columns than experts (E of them are read)"""
         T = z.shape[0]
         E = z.shape[1] if E is None else E
         idx, wgt = self.empty((T, top), torch.int32), self.empty((T, top))
         self._ok(self.lib.b200_lm_router_group_topk(z.data_ptr(), z.stride(0), N.ptr(correction), E, top, int(n_groups),
-                                                    int(keep), idx.data_ptr(), wgt.data_ptr(), T, self.s),
+                                                    int(keep), int(softmax), int(group_max), idx.data_ptr(),
+                                                    wgt.data_ptr(), T, self.s),
                  "lm_router_group_topk")
         return idx, wgt
 
@@ -236,13 +244,14 @@ class LayerOps:
         self.tc_enabled = False
 
     def to_bf16(self, X: torch.Tensor, K: int, rows: Optional[int] = None, row_map: Optional[torch.Tensor] = None,
-                div: int = 1, relu2: bool = False) -> torch.Tensor:
-        """fp32 rows -> bf16 rows zero-padded to a multiple of 64 columns (the GEMM's k-block)"""
+                div: int = 1, relu2: bool = False, act: int = ACT_NONE) -> torch.Tensor:
+        """fp32 rows -> bf16 rows zero-padded to a multiple of 64 columns (the GEMM's k-block); act: an activation
+        before the rounding (ACT_RELU2, also `relu2`; ACT_GELU)"""
         rows = X.shape[0] if rows is None else rows
         Kp = (K + 63) // 64 * 64
         out = self.empty((rows, Kp), torch.bfloat16)
         self._ok(self.lib.b200_lm_rows_to_bf16(X.data_ptr(), X.stride(0), N.ptr(row_map), div, out.data_ptr(), Kp, rows,
-                                               K, Kp, int(relu2), self.s), "lm_rows_to_bf16")
+                                               K, Kp, ACT_RELU2 if relu2 else int(act), self.s), "lm_rows_to_bf16")
         return out
 
     def tc_gemm(self, Xb: torch.Tensor, W: torch.Tensor, Y: torch.Tensor, *, N_: int, K: int, ldw: Optional[int] = None,
@@ -357,39 +366,65 @@ class LayerOps:
         return both[:T], both[T:].view(len(segments), 2), len(segments)
 
     def short_conv(self, U: torch.Tensor, w: torch.Tensor, state: torch.Tensor, ctx, act: bool = False,
-                   bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """U (T, C) column range of projected rows; w (C, taps); state (slots, >= (taps-1) * C) fp32 view of the pool"""
+                   bias: Optional[torch.Tensor] = None, residual: bool = False) -> torch.Tensor:
+        """U (T, C) column range of projected rows; w (C, taps); state (slots, >= (taps-1) * C) fp32 view of the pool;
+        residual: the result is U + conv(U)"""
         T, C = U.shape
         first, seqs, G = ctx.seq_tables()
         Y = self.empty((T, C))
         self._ok(self.lib.b200_lm_short_conv(U.data_ptr(), U.stride(0), w.data_ptr(), Y.data_ptr(), Y.stride(0),
                                              state.data_ptr() if state.numel() else 0, state.stride(0), ctx.slot.data_ptr(),
                                              ctx.pos.data_ptr(),
-                                             first.data_ptr(), seqs.data_ptr(), G, C, w.shape[1], int(act), N.ptr(bias), T,
-                                             self.s),
+                                             first.data_ptr(), seqs.data_ptr(), G, C, w.shape[1], int(act), N.ptr(bias),
+                                             int(residual), T, self.s),
                  "lm_short_conv")
         return Y
 
-    def qkv_post(self, Q, K, V, cache_layer, slot, pos, cs, H, G, dim, vdim, rot_dims):
-        """Q rotated in place; cache_layer (slots, capacity, >= G * (dim + vdim)) gets the rotated K and V of the rows"""
+    def token_shift(self, h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, ctx) -> torch.Tensor:
+        """-> M (n_mix, T, C): M[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s]; state (slots, C) fp32 view of the pool: the
+        last input of every slot's sequence (read by the first token of a step, then replaced)"""
+        T, C = h.shape
+        first, seqs, G = ctx.seq_tables()
+        M = self.empty((mu.shape[0], T, C))
+        self._ok(self.lib.b200_lm_token_shift(h.data_ptr(), h.stride(0), mu.data_ptr(), M.data_ptr(), M.stride(1), M.stride(0),
+                                              state.data_ptr(), state.stride(0), ctx.slot.data_ptr(), ctx.pos.data_ptr(),
+                                              first.data_ptr(), seqs.data_ptr(), G, C, mu.shape[0],
+                                              int(ctx.segments is None), T, self.s), "lm_token_shift")
+        return M
+
+    def qkv_post(self, Q, K, V, cache_layer, slot, pos, cs, H, G, dim, vdim, rot_dims, *, q_norm=None, k_norm=None,
+                 eps: float = 0.0, v_unit: bool = False, q_temp: Optional[tuple] = None, vmix=None, v_first=None, v_keep=None):
+        """Q rotated in place; cache_layer (slots, capacity, >= G * (dim + vdim)) gets the rotated K and V of the rows.
+        Before that: q_norm / k_norm: RMS norm over the whole projection times these weights; q_temp (coef, every): Q times
+        1 + coef ln(floor((pos + 1) / every) + 1); v_unit: every value head over its root mean square; vmix (one
+        number lam) with v_first (T, G vdim): V <- (1 - lam) V + lam v_first; v_keep (T, G vdim): gets the cached values"""
         self._ok(self.lib.b200_lm_qkv_post(Q.data_ptr(), Q.stride(0), K.data_ptr(), K.stride(0), V.data_ptr(), V.stride(0),
                                            cache_layer.data_ptr(), int(cache_layer.dtype == torch.bfloat16),
                                            cache_layer.stride(0), cache_layer.stride(1), slot.data_ptr(), pos.data_ptr(),
-                                           cs.data_ptr(), H, G, dim, vdim, rot_dims, Q.shape[0], self.s), "lm_qkv_post")
+                                           cs.data_ptr(), H, G, dim, vdim, rot_dims, N.ptr(q_norm), N.ptr(k_norm), float(eps),
+                                           int(v_unit), float(q_temp[0]) if q_temp else 0.0, int(q_temp[1]) if q_temp else 0,
+                                           N.ptr(vmix), N.ptr(v_first), v_first.stride(0) if v_first is not None else 0,
+                                           N.ptr(v_keep), v_keep.stride(0) if v_keep is not None else 0, Q.shape[0], self.s),
+                 "lm_qkv_post")
 
     def sink_attention(self, Q, cache_layer, slot, pos, out, sink, H, G, dim, vdim, scale, chunk=0, window=0,
-                       n_split=None):
-        """n_split None: enough blocks per (token, kv head) to fill the GPU when the step has few tokens, 1 for prompts"""
+                       n_split=None, bias_exp: float = 0.0, unit_sink: bool = False):
+        """n_split None: enough blocks per (token, kv head) to fill the GPU when the step has few tokens, 1 for prompts;
+        bias_exp > 0: 2^(-bias_exp (h + 1) / H) times the distance to the key is taken off head h's scores; unit_sink:
+        the softmax's denominator also holds 1"""
         T = Q.shape[0]
         if n_split is None:
             rep = H // G
             groups = T * G * ((rep + 7) // 8)
             n_split = max(1, min(64, (2 * SM_COUNT) // groups))
+            if window > 0:       # a window holds at most this many key tiles (of 32): more splits would only be merged
+                n_split = min(n_split, (window + 31) // 32)
         part = self.empty((T, H, n_split, vdim + 2)) if n_split > 1 else None
         self._ok(self.lib.b200_lm_sink_attention(
             Q.data_ptr(), Q.stride(0), cache_layer.data_ptr(), int(cache_layer.dtype == torch.bfloat16),
             cache_layer.stride(0), cache_layer.stride(1), slot.data_ptr(), pos.data_ptr(), out.data_ptr(), out.stride(0),
-            N.ptr(sink), H, G, dim, vdim, float(scale), int(chunk), int(window), N.ptr(part), n_split, T, self.s),
+            N.ptr(sink), H, G, dim, vdim, float(scale), int(chunk), int(window), float(bias_exp), int(unit_sink),
+            N.ptr(part), n_split, T, self.s),
             "lm_sink_attention")
 
     def heads_to_bf16(self, q: torch.Tensor, rep: int, dim: int) -> torch.Tensor:
@@ -400,23 +435,33 @@ class LayerOps:
                  "lm_heads_to_bf16")
         return out
 
-    def sink_softmax_bf16(self, S, pos, rep, sink, scale, chunk, window, key0, P):
+    def sink_softmax_bf16(self, S, pos, rep, sink, scale, chunk, window, key0, P, bias_exp: float = 0.0, head0: int = 0,
+                          H: int = 1, unit_sink: bool = False):
+        """head0, H: the first head of the rows' group and the number of heads (they fix the slopes of the distance bias)"""
         self._ok(self.lib.b200_lm_sink_softmax_bf16(S.data_ptr(), S.stride(0), pos.data_ptr(), rep, N.ptr(sink), float(scale),
-                                                    int(chunk), int(window), int(key0), P.data_ptr(), P.stride(0),
+                                                    int(chunk), int(window), int(key0), float(bias_exp), int(head0), int(H),
+                                                    int(unit_sink), P.data_ptr(), P.stride(0),
                                                     S.shape[0], P.shape[1], self.s), "lm_sink_softmax_bf16")
 
     def linear_state(self, q, k, v, out, state, ctx, *, H, rep, dim, vdim, act=False, unit_eps=0.0, q_scale=1.0,
-                     decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False, dt_in=False, skip=None):
-        """dt_in: the state-space form, u = softplus(a + dt_bias) v; skip (H,): out += skip[h] v"""
+                     decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False, dt_in=False, skip=None,
+                     decay_logits=None, bonus=None):
+        """dt_in: the state-space form, u = softplus(a + dt_bias) v; skip (H,): out += skip[h] v;
+        decay_logits (T, H dim) with bonus (H, dim): a decay per key channel w = exp(-exp(decay_logits)) and
+        out = S^T q + (sum_i q_i bonus_i k_i) v with S the state before the token, then S <- diag(w) S + k v^T"""
         _, seqs, G = ctx.seq_tables()
         T, Hk = q.shape[0], H // rep
         # a prompt step does the per-token work (activation, unit lengths, k . q, decay, beta) in one parallel pass first
-        prep = self.empty((T * (2 * Hk * dim + Hk + 2 * H),)) if T > SKINNY_ROWS else None
+        if decay_logits is not None:
+            prep = self.empty((T * (3 * H * dim + H),))
+        else:
+            prep = self.empty((T * (2 * Hk * dim + Hk + 2 * H),)) if T > SKINNY_ROWS else None
         self._ok(self.lib.b200_lm_linear_state(
             q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
             state.data_ptr(), state.stride(0), seqs.data_ptr(), G, ctx.slot.data_ptr(), ctx.pos.data_ptr(), H, rep, dim,
             vdim, int(act), float(unit_eps), float(q_scale), N.ptr(decay_const), N.ptr(a), a.stride(0) if a is not None else 0,
             N.ptr(A_log), N.ptr(dt_bias), N.ptr(b), b.stride(0) if b is not None else 0, int(delta), int(dt_in), N.ptr(skip),
+            N.ptr(decay_logits), decay_logits.stride(0) if decay_logits is not None else 0, N.ptr(bonus),
             N.ptr(prep), T, self.s),
             "lm_linear_state")
 
@@ -428,22 +473,25 @@ class LayerOps:
                                             int(gate_per_head), int(gate_silu), dv, n, float(scale), out.data_ptr(),
                                             out.stride(0), int(gate_first), T, self.s), "lm_head_post")
 
-    def glu_clamp(self, G, U, limit, alpha, Y, up_offset: float = 1.0):
-        """Y = g sigmoid(alpha g) (u + up_offset), g = min(G, limit), u = clamp(U, +-limit); limit inf, alpha 1 and
-        up_offset 0 give the plain silu-gated unit"""
+    def glu_clamp(self, G, U, limit, alpha, Y, up_offset: float = 1.0, cubic: float = 0.0):
+        """Y = g sigmoid(alpha (g + cubic g^3)) (u + up_offset), g = min(G, limit), u = clamp(U, +-limit); limit inf,
+        alpha 1 and up_offset 0 give the plain silu-gated unit; GELU_TANH_ALPHA and GELU_TANH_CUBIC the tanh form of gelu"""
         T, n = G.shape
         self._ok(self.lib.b200_lm_glu_clamp(G.data_ptr(), G.stride(0), U.data_ptr(), U.stride(0), float(limit),
-                                            float(alpha), float(up_offset), Y.data_ptr(), Y.stride(0), n, T, self.s),
+                                            float(alpha), float(cubic), float(up_offset), Y.data_ptr(), Y.stride(0), n, T,
+                                            self.s),
                  "lm_glu_clamp")
 
-    def glu_clamp_bf16(self, G, U, limit, alpha, up_offset: float = 1.0, live: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def glu_clamp_bf16(self, G, U, limit, alpha, up_offset: float = 1.0, live: Optional[torch.Tensor] = None,
+                       cubic: float = 0.0) -> torch.Tensor:
         """the gated activation written as bf16 operand rows (T, ceil64(n)) of the next tensor-core product; live (T,)
         int32: rows with a negative entry (padding of sorted expert segments) become zeros without being read"""
         T, n = G.shape
         Kp = (n + 63) // 64 * 64
         Y = self.empty((T, Kp), torch.bfloat16)
         self._ok(self.lib.b200_lm_glu_clamp_bf16(G.data_ptr(), G.stride(0), U.data_ptr(), U.stride(0), float(limit),
-                                                 float(alpha), float(up_offset), Y.data_ptr(), n, Kp, N.ptr(live), T, self.s),
+                                                 float(alpha), float(cubic), float(up_offset), Y.data_ptr(), n, Kp,
+                                                 N.ptr(live), T, self.s),
                  "lm_glu_clamp_bf16")
         return Y
 
