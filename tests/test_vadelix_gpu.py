@@ -322,7 +322,7 @@ def test_far_key_sink_and_distance_bias():
     H, G, d, dv, T = 3, 1, 12, 10, 750
     q, k, v = torch.randn(T, H, d, generator=g), 0.1 * torch.randn(T, G, d, generator=g), torch.randn(T, G, dv, generator=g)
     k[40, 0] = 25.0 * q[T - 1, 1] / q[T - 1, 1].norm()
-    sink = bf(torch.tensor([0.3, -1.0, 40.0]))
+    sink = bf(torch.tensor([0.3, -1.0, 300.0]))
     for n_split in (1, 8):
         got = _attend(eng, q, k, v, H, G, d, dv, 0.7, sink=sink, n_split=n_split)
         want = _attend_ref(q, k, v, H, G, 0.7, sink=sink.double())
@@ -330,8 +330,11 @@ def test_far_key_sink_and_distance_bias():
         assert (got[T - 1, 1] - v[40, 0].double()).abs().max() < 1e-3          # the far key
         assert got[:, 2].abs().max() < 1e-6                                      # the sink took everything
     # cached rows rounded to bf16 (the serving mode's cache) and a first position that is not a tile's start
+    # (the 29 rows before it are zeros in the cache: keys with score 0 and no value)
     got = _attend(eng, q[:90], bf(k[:90]), bf(v[:90]), H, G, d, dv, 0.7, pos0=29, sink=sink, dtype=torch.bfloat16)
-    assert (got - _attend_ref(q[:90], bf(k[:90]), bf(v[:90]), H, G, 0.7, sink=sink.double())).abs().max() < 2e-5
+    pad = lambda t: torch.cat([torch.zeros(29, *t.shape[1:]), t])
+    want = _attend_ref(pad(q[:90]), pad(bf(k[:90])), pad(bf(v[:90])), H, G, 0.7, sink=sink.double())[29:]
+    assert (got - want).abs().max() < 2e-5
     slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float64)
     kk = torch.zeros(T, G, d)
     got = _attend(eng, q, kk, v, H, G, d, dv, 0.7, bias_exp=8.0, unit_sink=True)
@@ -413,7 +416,7 @@ def test_state_with_a_decay_per_channel_in_portions_and_slots(H, d):
     st = pool.state[:, 4:4 + sf]
 
     def run(ctx, parts):
-        r, k, v, x = (dev(torch.cat(p)) for p in zip(*parts))
+        r, k, v, x = (dev(torch.cat(p)) for p in parts)
         o = dev(torch.zeros(r.shape[0], n))
         ops.linear_state(r, k, v, o, st, ctx, H=H, rep=1, dim=d, vdim=d, decay_logits=x, bonus=dev(u, torch.bfloat16))
         return host(eng, o)
@@ -464,7 +467,8 @@ def test_gelu_forms():
     assert (y - O.gelu_erf(x.double() @ w.double().T)).abs().max() < 1e-5
     big = torch.randn(130, K, generator=g) * 3
     hb = host(eng16, eng16.ops.to_bf16(dev(big), K, act=ACT_GELU))
-    assert (hb[:, :K] - O.gelu_erf(big.double())).abs().max() < 2e-2 and hb[:, K:].abs().max() == 0
+    want = O.gelu_erf(big.double())
+    assert ((hb[:, :K] - want).abs() <= want.abs() / 256 + 1e-6).all() and hb[:, K:].abs().max() == 0
     a, b = torch.randn(T, n, generator=g) * 3, torch.randn(T, n, generator=g)
     out = dev(torch.zeros(T, n))
     eng.ops.glu_clamp(dev(a), dev(b), float("inf"), GELU_TANH_ALPHA, out, up_offset=0.0, cubic=GELU_TANH_CUBIC)
@@ -613,7 +617,7 @@ def test_long_prompt_paths_of_the_serving_mode():
     cfg = config([layer("attention_2", att2(heads=4, kv_heads=2, dim=16, vdim=16, window=150), moe(experts=8, top=2, ff=32, count=2, keep=1)),
                   layer("wkv", wkv(heads=4, dim=16)),
                   layer("attention", att(heads=4, kv_heads=2, dim=24, vdim=16, dims=16), "dense"),
-                  layer("attention_2", att2(heads=2, kv_heads=1, dim=8, vdim=16, window=40, v_mix=True), "dense")], width=64, groups=4)
+                  layer("attention_2", att2(heads=2, kv_heads=1, dim=8, vdim=16, window=40, v_mix=False), "dense")], width=64, groups=4)
     model, W = build(cfg, "bfloat16", seed=4)
     exact, _ = build(cfg, "float32", seed=4)
     lm, eng = model.language_model, model.engine
