@@ -511,7 +511,7 @@ def c4_leg(dev, args):
 
 
 # ------------------------------------------------------------------------------------------------------------
-# `--design buzopel | sonulorn | lilosun`: prefill and decode throughput of a decoder design assembled from decoder_blocks
+# `--design buzopel | sonulorn | lilosun | vadelix`: prefill and decode throughput of a decoder design assembled from decoder_blocks
 # over the layer ops (Buzopel: latent attention + expert mixture; Sonulorn: sink attention, matrix-state mixers and a
 # clamped gated feed-forward behind one shared input projection; Lilosun: windowed gated latent attention and state-space
 # mixers in scaled pre-norm layers with a grouped expert mixture — also beside Buzopel, the closest design on the same
@@ -652,10 +652,64 @@ def _lilosun_account(m, z, T):
     return act_w, other, mix_flops
 
 
+# Vadelix beside Lilosun (the closest design on the same engine: pre-norm layers, windowed attention and a matrix-state
+# mixer in turn, a dense unit and a grouped expert mixture with a shared expert) at equal width, depth, head sizes,
+# window, experts and expert size.  The keys that only Lilosun's configuration reads ride in the same size table.
+VADELIX_SIZES = {
+    "2048w": dict(LILOSUN_SIZES["2048w"], kv_heads=4, wkv_heads=32, wkv_dim=64, decay_rank=64, norm_groups=8, taps=4),
+    "4096w": dict(LILOSUN_SIZES["4096w"], kv_heads=8, wkv_heads=64, wkv_dim=64, decay_rank=64, norm_groups=8, taps=4),
+}
+
+
+def _vadelix_config(z):
+    H, G, d = z["heads"], z["kv_heads"], z["dim"]
+    att2 = {"heads": H, "kv_heads": G, "dim": d, "vdim": z["vdim"], "mask": {"size": z["window"]}, "scale": d ** -0.5,
+            "q_temp": {"coef": 0.1, "every": 1024}, "v_mix": True}
+    att = {"heads": H, "kv_heads": G, "dim": d, "vdim": z["vdim"], "scale": d ** -0.5, "v_mix": True,
+           "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    wkv = {"heads": z["wkv_heads"], "dim": z["wkv_dim"], "decay_rank": z["decay_rank"]}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["expert_groups"], "keep": z["keep"]}}}
+    layers = [{"type": "attention_2", "mixer": att2, "mlp": {"kind": "dense", "ff": z["dense_ff"]}},
+              {"type": "wkv", "mixer": wkv, "mlp": moe}, {"type": "attention", "mixer": att, "mlp": moe},
+              {"type": "wkv", "mixer": wkv, "mlp": moe}]
+    return {"architecture": "Vadelix", "vocab": z["vocab"], "width": z["width"], "layers": layers[:z["layers"]],
+            "norm": {"eps": 1e-6, "groups": z["norm_groups"]}, "residual_mult": 0.5, "canon": {"taps": z["taps"]}}
+
+
+def _vadelix_model(z, dev):
+    from mlx_vlm_b200.models.vadelix import Model as VModel, ModelConfig as VConfig
+    return VModel(VConfig.from_dict(_vadelix_config(z)), device=dev).init_random(0)
+
+
+def _vadelix_account(m, z, T):
+    from mlx_vlm_b200.models.decoder_blocks import GatedDense, GroupedAttention
+    W = z["width"]
+    act_w, other, mix_flops = 0, 8 * m.state_floats, 0.0      # the fp32 state is read and written once per token
+    for L in m.layers:
+        x = L.mixer
+        act_w += W * L.taps
+        if isinstance(x, GroupedAttention):
+            act_w += (x.n_q + x.n_k + x.n_v) * W + W * x.H * x.vdim
+            mean_seen = sum(min(p + 1, x.window or p + 1) for p in range(T)) / T
+            mix_flops += 2 * x.H * (x.dim + x.vdim) * mean_seen
+            other += 2 * x.kv_dim * min(x.window or T, T)      # cached rows a decoded token reads
+        else:
+            act_w += 4 * x.n * W + x.rank * W + x.n * x.rank + W * x.n
+            mix_flops += 4 * x.H * x.dim * x.dim
+        f = L.ff
+        if isinstance(f, GatedDense):
+            act_w += 3 * f.ff * W
+        elif f is not None:
+            act_w += f.E * W + 2 * f.top * f.ff * W + (2 * f.shared.ff * W if f.shared else 0)
+    return act_w, other, mix_flops
+
+
 # design -> (sizes, model factory, byte / flop accounting, closest design on the same engine measured beside it or None)
 DESIGNS = {"buzopel": (DESIGN_SIZES, _buzopel_model, _buzopel_account, None),
            "sonulorn": (SONULORN_SIZES, _sonulorn_model, _sonulorn_account, None),
-           "lilosun": (LILOSUN_SIZES, _lilosun_model, _lilosun_account, ("buzopel_equal_size", _buzopel_model, _buzopel_account))}
+           "lilosun": (LILOSUN_SIZES, _lilosun_model, _lilosun_account, ("buzopel_equal_size", _buzopel_model, _buzopel_account)),
+           "vadelix": (VADELIX_SIZES, _vadelix_model, _vadelix_account, ("lilosun_equal_size", _lilosun_model, _lilosun_account))}
 
 
 def _measure_layered(m, account, z, T, n_dec, rows, ids, args, timed, hbm, tpk):
@@ -786,7 +840,7 @@ def main():
     ap.add_argument("--no-mega", action="store_true")
     ap.add_argument("--mega-mode", type=int, default=None,
                     help="decode kernel: 0 per-phase kernels, 1 k_mega (CUDA cores), 2 k_mega_tc (tcgen05)")
-    ap.add_argument("--design", default=None, choices=["buzopel", "sonulorn", "lilosun"],
+    ap.add_argument("--design", default=None, choices=["buzopel", "sonulorn", "lilosun", "vadelix"],
                     help="instead of the default workload: prefill / decode throughput of this decoder design at "
                          "layer sizes of real models, beside the closest existing model at equal size")
     ap.add_argument("--design-sizes", default="", help="comma-separated subset of the sizes (default: all)")

@@ -494,7 +494,7 @@ int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cach
  * dt_in (state-space form): u = softplus(a + dt_bias) v; skip != NULL ([H], bf16): out += skip[h] v.
  * prep != NULL (a prompt step; T tokens): scratch of T * (2 (H / rep) dim + H / rep + 2 H) floats — the per-token work
  * (activation, unit lengths, k . q, decay, beta) runs first as one parallel pass and the walk reads its results.
- * wraw != NULL ([T][H dim]; needs prep of T * (3 H dim + H) floats, rep 1): a decay per key channel w = exp(-exp(wraw))
+ * wraw != NULL ([T][H dim]; prep, if given, of T * (3 H dim + H) floats; rep 1): a decay per key channel w = exp(-exp(wraw))
  * and a bonus (bf16 [H][dim]) for the current token: out = S^T q + (sum_i q_i bonus_i k_i) v, then S <- diag(w) S + k v^T */
 int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv, float* out, long ldo,
                          float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,

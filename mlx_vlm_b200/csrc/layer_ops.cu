@@ -777,7 +777,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemm_skinny_vec_kernel(GemmRows
 // Operands of the tensor-core products of a prompt step (bf16 serving mode; the products themselves are the
 // weight-major tcgen05 GEMM with fp32 output, b200_gemm_wt_f32):
 // rows of fp32 numbers -> bf16 rows padded with zeros to Kp columns; optional gather (src row = map[i] / div),
-// optional activation before the rounding (1: relu^2, 2: the exact gelu); with `dst_map` the kernel instead scatters fp32 rows (dst row = dst_map[i])
+// optional activation before the rounding (1: relu^2, 2: the exact gelu, 3: tanh); with `dst_map` the kernel instead scatters fp32 rows (dst row = dst_map[i])
 __global__ void rows_to_bf16_kernel(const float* __restrict__ X, long ldx, const int* __restrict__ map, int div,
                                     bf16* __restrict__ out, long ldo, int K, int Kp, int relu2) {
   const int i = blockIdx.x;
@@ -787,6 +787,7 @@ __global__ void rows_to_bf16_kernel(const float* __restrict__ X, long ldx, const
     float v = (k < K && src >= 0) ? x[k] : 0.f;
     if (relu2 == 1) { v = fmaxf(v, 0.f); v *= v; }
     else if (relu2 == 2) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    else if (relu2 == 3) v = tanhf(v);
     out[(long)i * ldo + k] = f2bf(v);
   }
 }
@@ -802,6 +803,8 @@ __global__ void rows_to_bf16x4_kernel(const float* __restrict__ X, long ldx, con
     if (relu2 == 2) {
       v.x = 0.5f * v.x * (1.0f + erff(v.x * 0.70710678118654752f)); v.y = 0.5f * v.y * (1.0f + erff(v.y * 0.70710678118654752f));
       v.z = 0.5f * v.z * (1.0f + erff(v.z * 0.70710678118654752f)); v.w = 0.5f * v.w * (1.0f + erff(v.w * 0.70710678118654752f));
+    } else if (relu2 == 3) {
+      v.x = tanhf(v.x); v.y = tanhf(v.y); v.z = tanhf(v.z); v.w = tanhf(v.w);
     } else if (relu2 == 1) {
       v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
       v.x *= v.x; v.y *= v.y; v.z *= v.z; v.w *= v.w;

@@ -419,9 +419,11 @@ struct StateP {
   int delta;
   int dt_in;                        // state-space form: beta = softplus(a[t][h] + dt_bias[h]) (the step size) and u = beta v
   const bf16* skip;                 // [H] or NULL: o += skip[h] v
-  // decay per key channel (the template's CHAN; always prepared):  o = S^T q + (sum_i q_i bonus_i k_i) v  with S the state
-  // BEFORE the token, then  S <- diag(w) S + k v^T;  wdec [T][H dim] holds w, kq_in the bracket
+  // decay per key channel (the template's CHAN):  o = S^T q + (sum_i q_i bonus_i k_i) v  with S the state BEFORE the
+  // token, then  S <- diag(w) S + k v^T.  Prepared: wdec [T][H dim] holds w and kq_in the bracket; else wdec holds the
+  // logits x of w = exp(-exp(x)) and the bracket is made here from `bonus` ([H][dim])
   const float* wdec; long ldw;
+  const bf16* bonus;
 };
 // The per-token work of a prompt step in one parallel pass: q, k activated and scaled to unit length (a warp per
 // token and q/k head, the same order of sums as the walk's own staging), k . q, the decay and beta of every head.
@@ -532,7 +534,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     if ((int)threadIdx.x < nc) {
       const long t = start + c0 + threadIdx.x;
       if (CHAN) {
-        rkq = p.kq_in[t * (p.H / p.rep) + hk];
+        if (p.kq_in) rkq = p.kq_in[t * (p.H / p.rep) + hk];
       } else if (p.kq_in) {
         ra = p.dec_in[t * p.H + h]; rb = p.bet_in[t * p.H + h]; rkq = p.kq_in[t * (p.H / p.rep) + hk];
       } else {
@@ -541,7 +543,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       }
     }
   };
-  const float A = (p.decay_const || !raw) ? 0.f : expf(bf2f(p.A_log[h])), dtb = (p.decay_const || !raw) ? 0.f : bf2f(p.dt_bias[h]);
+  const float A = (CHAN || p.decay_const || !raw) ? 0.f : expf(bf2f(p.A_log[h])), dtb = (CHAN || p.decay_const || !raw) ? 0.f : bf2f(p.dt_bias[h]);
   const float dconst = p.decay_const ? p.decay_const[h] : 0.f;
   const float skip = p.skip ? bf2f(p.skip[h]) : 0.f;
   request(0);
@@ -554,7 +556,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       if (e < CT * DKP) {
         ks[tk][(i / LS_R) * LS_RS + (i % LS_R)] = act_qk ? silu_exact(rk[n]) : rk[n];
         qs[tk][(i / LS_R) * LS_RS + (i % LS_R)] = act_qk ? silu_exact(rq[n]) : rq[n];
-        if (CHAN) ws[tk][(i / LS_R) * LS_RS + (i % LS_R)] = rw[n];
+        if (CHAN) ws[tk][(i / LS_R) * LS_RS + (i % LS_R)] = raw ? expf(-expf(rw[n])) : rw[n];
       }
     }
 #pragma unroll
@@ -563,7 +565,9 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       if (e < CT * CB) vs[e / CB][e % CB] = p.act ? silu_exact(rv[n]) : rv[n];
     }
     if ((int)threadIdx.x < nc) {
-      if (raw) {
+      if (CHAN) {
+        if (!raw) kq[threadIdx.x] = rkq;
+      } else if (raw) {
         const float dt = p.decay_const ? 0.f : softplus_exact(ra + dtb);
         dec[threadIdx.x] = p.decay_const ? dconst : expf(-A * dt);
         bet[threadIdx.x] = p.dt_in ? dt : (p.b ? sigmoid_exact(rb) : 1.f);
@@ -588,7 +592,7 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
         const int at = (i / LS_R) * LS_RS + (i % LS_R);
         const float a = ks[tk][at] * ik, b = qs[tk][at] * iq;
         ks[tk][at] = a; qs[tk][at] = b;
-        dot = fmaf(a, b, dot);
+        dot = CHAN ? fmaf(a * b, bf2f(p.bonus[(long)hk * p.dim + i]), dot) : fmaf(a, b, dot);
       }
       dot = warp_sum(dot);
       if (lane == 0) kq[tk] = dot;
@@ -936,11 +940,11 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
   B200_REQUIRE(dim > 0 && dim <= 32 * LS_R && vdim > 0, "lm_linear_state: key size %d not supported (at most %d)", dim, 32 * LS_R);
   const bool chan = wraw != nullptr;
   B200_REQUIRE(chan || decay_const || (a && A_log && dt_bias), "lm_linear_state: a decay per head, or the inputs of a computed one");
-  B200_REQUIRE(!chan || (bonus && prep && rep == 1 && !delta && !dt_in && !act && unit_eps == 0.f && !skip && !decay_const),
-               "lm_linear_state: a decay per key channel comes with a bonus, prepared inputs and nothing else");
+  B200_REQUIRE(!chan || (bonus && rep == 1 && !delta && !dt_in && !act && unit_eps == 0.f && !skip && !decay_const),
+               "lm_linear_state: a decay per key channel comes with a bonus and nothing else");
   B200_REQUIRE(!dt_in || (!decay_const && !delta && !b), "lm_linear_state: the step size scales the input only in the plain form with a computed decay");
   StateP p{q, ldq, k, ldk, v, ldv, out, ldo, state, slot_stride, seqs, slot, pos, H, rep, dim, vdim, act, unit_eps, q_scale,
-           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta, dt_in, (const bf16*)skip, nullptr, 0};
+           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta, dt_in, (const bf16*)skip, wraw, ldwr, (const bf16*)bonus};
   const cudaStream_t cs = (cudaStream_t)st;
   if (prep) {     // scratch of T * (2 Hk dim + Hk + 2 H) floats: the per-token work runs first, over all tokens at once
     B200_REQUIRE(T > 0, "lm_linear_state: the prepared path needs the number of tokens");

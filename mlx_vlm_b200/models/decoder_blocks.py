@@ -53,7 +53,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .._native import B200Error as _B200Error
-from .layer_ops import ACT_GELU, EPI_GELU, EPI_RELU2, EPI_SOFTCAP, GELU_TANH_ALPHA, GELU_TANH_CUBIC, LayerOps
+from .layer_ops import ACT_GELU, ACT_TANH, EPI_GELU, EPI_RELU2, EPI_SOFTCAP, GELU_TANH_ALPHA, GELU_TANH_CUBIC, LayerOps
 
 
 @dataclass
@@ -1241,8 +1241,18 @@ class TokenShiftState:
                 ops.linear(M[i], w["rkvg"][i], out=D[:, i * n:(i + 1) * n])
         else:                         # few rows: ONE launch over the four (input, weight) pairs
             ops.gemm(M, w["rkvg"], D, M=T, N_=n, K=W, ldx=W, xb=T * W, wb=n * W, ldy=4 * n, yb=n, batch=4)
-        lat = ops.linear(M[4], w["w1"], epi=EPI_SOFTCAP, epi_param=1.0)    # tanh
-        logit = ops.linear(lat, w["w2"], bias=w["w0"])
+        logit = None
+        if ops.tc_ok(T, W, self.rank):    # a prompt: the tanh is applied while the latent rows are rounded to the operand
+            try:
+                logit = ops.empty((T, n))
+                ops.tc_gemm(ops.to_bf16(ops.linear(M[4], w["w1"]), self.rank, act=ACT_TANH), w["w2"], logit, N_=n, K=self.rank,
+                            bias=w["w0"])
+            except _B200Error as e:
+                ops.tc_refused(e)
+                logit = None
+        if logit is None:
+            lat = ops.linear(M[4], w["w1"], epi=EPI_SOFTCAP, epi_param=1.0)    # tanh
+            logit = ops.linear(lat, w["w2"], bias=w["w0"])
         o = ops.empty((T, n))
         ops.linear_state(D[:, :n], D[:, n:2 * n], D[:, 2 * n:3 * n], o, st[:, off + W:off + self.state_floats], ctx, H=self.H,
                          rep=1, dim=self.dim, vdim=self.dim, decay_logits=logit, bonus=w["u"])

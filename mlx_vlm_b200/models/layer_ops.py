@@ -16,7 +16,7 @@ import torch
 from .. import _native as N
 
 EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_ADD, EPI_SCALE, EPI_GELU = 0, 1, 2, 3, 4, 5
-ACT_NONE, ACT_RELU2, ACT_GELU = 0, 1, 2     # activation codes of `to_bf16` (gelu: the exact, erf form)
+ACT_NONE, ACT_RELU2, ACT_GELU, ACT_TANH = 0, 1, 2, 3     # activation codes of `to_bf16` (gelu: the exact, erf form)
 GELU_TANH_ALPHA, GELU_TANH_CUBIC = 1.5957691216057308, 0.044715     # z sigmoid(alpha (z + cubic z^3)) = the tanh form of gelu
 SM_COUNT = 148
 TC_MIN_ROWS = 128     # from this many rows on, a product of the bf16 serving mode runs on the tcgen05 GEMM
@@ -246,7 +246,7 @@ class LayerOps:
     def to_bf16(self, X: torch.Tensor, K: int, rows: Optional[int] = None, row_map: Optional[torch.Tensor] = None,
                 div: int = 1, relu2: bool = False, act: int = ACT_NONE) -> torch.Tensor:
         """fp32 rows -> bf16 rows zero-padded to a multiple of 64 columns (the GEMM's k-block); act: an activation
-        before the rounding (ACT_RELU2, also `relu2`; ACT_GELU)"""
+        before the rounding (ACT_RELU2, also `relu2`; ACT_GELU; ACT_TANH)"""
         rows = X.shape[0] if rows is None else rows
         Kp = (K + 63) // 64 * 64
         out = self.empty((rows, Kp), torch.bfloat16)
@@ -453,7 +453,7 @@ class LayerOps:
         T, Hk = q.shape[0], H // rep
         # a prompt step does the per-token work (activation, unit lengths, k . q, decay, beta) in one parallel pass first
         if decay_logits is not None:
-            prep = self.empty((T * (3 * H * dim + H),))
+            prep = self.empty((T * (3 * H * dim + H),)) if T > SKINNY_ROWS else None
         else:
             prep = self.empty((T * (2 * Hk * dim + Hk + 2 * H),)) if T > SKINNY_ROWS else None
         self._ok(self.lib.b200_lm_linear_state(
