@@ -495,13 +495,17 @@ int b200_lm_sink_attention(const float* q, long ldq, const void* cache, int cach
  * prep != NULL (a prompt step; T tokens): scratch of T * (2 (H / rep) dim + H / rep + 2 H) floats — the per-token work
  * (activation, unit lengths, k . q, decay, beta) runs first as one parallel pass and the walk reads its results.
  * wraw != NULL ([T][H dim]; prep, if given, of T * (3 H dim + H) floats; rep 1): a decay per key channel w = exp(-exp(wraw))
- * and a bonus (bf16 [H][dim]) for the current token: out = S^T q + (sum_i q_i bonus_i k_i) v, then S <- diag(w) S + k v^T */
+ * and a bonus (bf16 [H][dim]) for the current token: out = S^T q + (sum_i q_i bonus_i k_i) v, then S <- diag(w) S + k v^T.
+ * With it, prep and n_parts > 1: every sequence is walked in parts of part_len tokens at the same time (the state is linear
+ * in its start: a first pass leaves every part's own contribution and decay product, a small launch chains them into the
+ * parts' start states, a second pass walks every part from its start state); n_parts >= the parts of the longest
+ * sequence, part_scratch: n_seq * n_parts * (H * 8 * vdim * lanes + H * lanes * 8) floats, lanes = the state layout's */
 int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, const float* v, long ldv, float* out, long ldo,
                          float* state, long slot_stride, const int* seqs, int n_seq, const int* slot, const int* pos,
                          int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
                          const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
                          const float* b, long ldb, int delta, int dt_in, const void* skip, const float* wraw, long ldwr,
-                         const void* bonus, float* prep, int T, void* stream);
+                         const void* bonus, float* prep, int part_len, int n_parts, float* part_scratch, int T, void* stream);
 /* operands of the tensor-core attention of a prompt step: out[(t, r)] = bf16 of q[t][r * dim .. + dim) padded to Kp;
  * P[(t, r)][j] = softmax over the visible keys key0 + j (and sink[r]) of scale * S[(t, r)][j], bf16, zero elsewhere */
 int b200_lm_heads_to_bf16(const float* q, long ldq, int rep, int dim, void* out, int Kp, int T, void* stream);

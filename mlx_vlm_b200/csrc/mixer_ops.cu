@@ -424,6 +424,14 @@ struct StateP {
   // logits x of w = exp(-exp(x)) and the bracket is made here from `bonus` ([H][dim])
   const float* wdec; long ldw;
   const bf16* bonus;
+  // A long sequence in parts that are walked at the same time (decay per key channel, prepared inputs).  The state is
+  // linear in its start: after a part,  S_end = diag(prod of the part's w) S_start + S_local  with S_local the part
+  // walked from zero.  Pass 1 (the template's LOCAL) walks every part but a sequence's last from zero, without outputs,
+  // and leaves S_local and the product of its decays; a small launch chains them into every part's true start state;
+  // pass 2 walks every part from that state with outputs, and the last part leaves the slot's state.
+  int part_len, n_parts;            // n_parts > 0: blockIdx.x = sequence * n_parts + part
+  float* part_state;                // [n_seq][n_parts][H LS_R vdim P]: S_local, then the start state of the part after
+  float* part_decay;                // [n_seq][n_parts][H][P LS_R]
 };
 // The per-token work of a prompt step in one parallel pass: q, k activated and scaled to unit length (a warp per
 // token and q/k head, the same order of sums as the walk's own staging), k . q, the decay and beta of every head.
@@ -485,7 +493,7 @@ __global__ void state_prep_kernel(StatePrepP p) {
   }
 }
 
-template <int P, bool DELTA, bool CHAN>
+template <int P, bool DELTA, bool CHAN, bool LOCAL = false>
 __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
   // Tokens are staged CT at a time.  The raw q, k, v, decay and beta inputs of the NEXT group are requested from
   // global memory into registers before the current group is walked, so their latency hides behind the walk.
@@ -499,14 +507,30 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
   __shared__ __align__(16) float ks[CT][LD], qs[CT][LD], ws[CHAN ? CT : 1][CHAN ? LD : 4];
   __shared__ float vs[CT][CB];
   __shared__ float dec[CT], bet[CT], kq[CT];
-  const int start = p.seqs[2 * blockIdx.x], rows = p.seqs[2 * blockIdx.x + 1];
+  const int seq = p.n_parts > 0 ? blockIdx.x / p.n_parts : blockIdx.x, part = p.n_parts > 0 ? blockIdx.x % p.n_parts : 0;
+  int start = p.seqs[2 * seq], rows = p.seqs[2 * seq + 1];
+  bool last_part = true;
+  if (p.n_parts > 0) {
+    const int n = (rows + p.part_len - 1) / p.part_len;          // parts of this sequence
+    if (part >= (LOCAL ? n - 1 : n)) return;                     // (whole block)
+    last_part = part == n - 1;
+    start += part * p.part_len;
+    rows = min(p.part_len, rows - part * p.part_len);
+  }
   const int h = blockIdx.y, hk = h / p.rep;
   const int cj = threadIdx.x / P, r = threadIdx.x % P, col = blockIdx.z * CB + cj;
   const bool valid = col < p.vdim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float S[LS_R];
+  float Dacc[LOCAL ? LS_R : 1];
+  if (LOCAL) {
+#pragma unroll
+    for (int i = 0; i < LS_R; ++i) Dacc[i] = 1.f;
+  }
+  const long head_floats = (long)LS_R * p.vdim * P;
   float* st = p.state + (long)p.slot[start] * p.slot_stride;
-  if (p.pos[start] > 0 && valid) {
+  if (!LOCAL && part > 0) st = p.part_state + ((long)seq * p.n_parts + part - 1) * p.H * head_floats;    // the start state made for this part
+  if (!LOCAL && (part > 0 || p.pos[start] > 0) && valid) {
 #pragma unroll
     for (int i = 0; i < LS_R; ++i) S[i] = st[(((long)h * LS_R + i) * p.vdim + col) * P + r];
   } else {
@@ -613,14 +637,19 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
         const float4 w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + 4);
         const float w_[LS_R] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
         wp += LD;
-        float b0 = 0.f, b1 = 0.f;
-#pragma unroll
-        for (int i = 0; i < LS_R; i += 2) { b0 = fmaf(S[i], q_[i], b0); b1 = fmaf(S[i + 1], q_[i + 1], b1); }
-        float dq = b0 + b1;
-#pragma unroll
-        for (int o = 1; o < P; o <<= 1) dq += __shfl_xor_sync(0xffffffffu, dq, o);
         const float vin = vs[tk][cj];
-        if (r == 0 && valid) *op = fmaf(vin, kq[tk], dq);
+        if (LOCAL) {
+#pragma unroll
+          for (int i = 0; i < LS_R; ++i) Dacc[i] *= w_[i];
+        } else {
+          float b0 = 0.f, b1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < LS_R; i += 2) { b0 = fmaf(S[i], q_[i], b0); b1 = fmaf(S[i + 1], q_[i + 1], b1); }
+          float dq = b0 + b1;
+#pragma unroll
+          for (int o = 1; o < P; o <<= 1) dq += __shfl_xor_sync(0xffffffffu, dq, o);
+          if (r == 0 && valid) *op = fmaf(vin, kq[tk], dq);
+        }
 #pragma unroll
         for (int i = 0; i < LS_R; ++i) S[i] = fmaf(k_[i], vin, w_[i] * S[i]);
         continue;
@@ -647,9 +676,42 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
       for (int i = 0; i < LS_R; ++i) S[i] = fmaf(k_[i], u, d * S[i]);
     }
   }
-  if (valid) {
+  if (LOCAL) {                       // what the part adds to any start state, and the product of its decays
+    float* sl = p.part_state + ((long)seq * p.n_parts + part) * p.H * head_floats;
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < LS_R; ++i) sl[(((long)h * LS_R + i) * p.vdim + col) * P + r] = S[i];
+    }
+    if (col == 0) {
+      float* dl = p.part_decay + (((long)seq * p.n_parts + part) * p.H + h) * (P * LS_R);
+#pragma unroll
+      for (int i = 0; i < LS_R; ++i) dl[r * LS_R + i] = Dacc[i];
+    }
+    return;
+  }
+  if (valid && last_part) {
+    st = p.state + (long)p.slot[start] * p.slot_stride;
 #pragma unroll
     for (int i = 0; i < LS_R; ++i) st[(((long)h * LS_R + i) * p.vdim + col) * P + r] = S[i];
+  }
+}
+// the start state of every part after a sequence's first: S <- diag(part's decay product) S + S_local, part after part
+__global__ void state_parts_chain_kernel(StateP p, int P) {
+  const int seq = blockIdx.x, h = blockIdx.y;
+  const int start = p.seqs[2 * seq], rows = p.seqs[2 * seq + 1];
+  const int n = (rows + p.part_len - 1) / p.part_len;
+  const long head_floats = (long)LS_R * p.vdim * P;
+  const float* st = p.state + (long)p.slot[start] * p.slot_stride + (long)h * head_floats;
+  const bool fresh = p.pos[start] == 0;
+  for (long e = (long)blockIdx.z * blockDim.x + threadIdx.x; e < head_floats; e += (long)blockDim.x * gridDim.z) {
+    const int i = (int)(e / ((long)p.vdim * P)), r = (int)(e % P);
+    float S = fresh ? 0.f : st[e];
+    for (int c = 0; c + 1 < n; ++c) {
+      const long at = (long)seq * p.n_parts + c;
+      float* sl = p.part_state + (at * p.H + h) * head_floats + e;
+      S = fmaf(p.part_decay[(at * p.H + h) * (P * LS_R) + r * LS_R + i], S, *sl);
+      *sl = S;
+    }
   }
 }
 
@@ -934,7 +996,7 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
                          int H, int rep, int dim, int vdim, int act, float unit_eps, float q_scale,
                          const float* decay_const, const float* a, long lda, const void* A_log, const void* dt_bias,
                          const float* b, long ldb, int delta, int dt_in, const void* skip, const float* wraw, long ldwr,
-                         const void* bonus, float* prep, int T, void* st) {
+                         const void* bonus, float* prep, int part_len, int n_parts, float* part_scratch, int T, void* st) {
   B200_REQUIRE(q && k && v && out && state && seqs && slot && pos && n_seq > 0 && H > 0 && rep > 0 && H % rep == 0,
                "lm_linear_state: bad argument");
   B200_REQUIRE(dim > 0 && dim <= 32 * LS_R && vdim > 0, "lm_linear_state: key size %d not supported (at most %d)", dim, 32 * LS_R);
@@ -944,7 +1006,7 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
                "lm_linear_state: a decay per key channel comes with a bonus and nothing else");
   B200_REQUIRE(!dt_in || (!decay_const && !delta && !b), "lm_linear_state: the step size scales the input only in the plain form with a computed decay");
   StateP p{q, ldq, k, ldk, v, ldv, out, ldo, state, slot_stride, seqs, slot, pos, H, rep, dim, vdim, act, unit_eps, q_scale,
-           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta, dt_in, (const bf16*)skip, wraw, ldwr, (const bf16*)bonus};
+           nullptr, nullptr, nullptr, decay_const, a, lda, (const bf16*)A_log, (const bf16*)dt_bias, b, ldb, delta, dt_in, (const bf16*)skip, wraw, ldwr, (const bf16*)bonus, 0, 0, nullptr, nullptr};
   const cudaStream_t cs = (cudaStream_t)st;
   if (prep) {     // scratch of T * (2 Hk dim + Hk + 2 H) floats: the per-token work runs first, over all tokens at once
     B200_REQUIRE(T > 0, "lm_linear_state: the prepared path needs the number of tokens");
@@ -960,10 +1022,18 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
     p.q = qn; p.ldq = n; p.k = kn; p.ldk = n; p.kq_in = kq; p.dec_in = dec; p.bet_in = bet;
   }
   const dim3 block(LS_THREADS);
+  const bool parts = chan && prep && n_parts > 1 && part_len > 0 && part_scratch;
 #define LS_LAUNCH(PP)                                                                                            \
   do {                                                                                                           \
     const dim3 grid(n_seq, H, cdiv(vdim, LS_THREADS / PP));                                                      \
-    if (chan) linear_state_kernel<PP, false, true><<<grid, block, 0, cs>>>(p);                                   \
+    if (parts) {     /* scratch: n_seq * n_parts * (H LS_R vdim PP + H PP LS_R) floats */                        \
+      p.part_len = part_len; p.n_parts = n_parts; p.part_state = part_scratch;                                   \
+      p.part_decay = part_scratch + (long)n_seq * n_parts * H * LS_R * vdim * PP;                                \
+      const dim3 pgrid(n_seq * n_parts, H, grid.z);                                                              \
+      linear_state_kernel<PP, false, true, true><<<pgrid, block, 0, cs>>>(p);                                    \
+      state_parts_chain_kernel<<<dim3(n_seq, H, cdiv(LS_R * vdim * PP, 1024)), 256, 0, cs>>>(p, PP);             \
+      linear_state_kernel<PP, false, true, false><<<pgrid, block, 0, cs>>>(p);                                   \
+    } else if (chan) linear_state_kernel<PP, false, true><<<grid, block, 0, cs>>>(p);                            \
     else if (delta) linear_state_kernel<PP, true, false><<<grid, block, 0, cs>>>(p);                             \
     else linear_state_kernel<PP, false, false><<<grid, block, 0, cs>>>(p);                                       \
   } while (0)

@@ -1189,6 +1189,7 @@ class TokenShiftState:
     S <- diag(w) S + k v^T.  Every head's o is divided by its root mean square, the heads side by side are multiplied by
     `norm` and the gate, then W_o."""
     MIXES = ("r", "k", "v", "g", "w")
+    PART_LEN = 256        # a prompt's sequences are walked in parts of this many tokens at the same time
 
     def __init__(self, index: int, cfg: dict, width: int):
         self.index, self.W = index, width
@@ -1255,7 +1256,7 @@ class TokenShiftState:
             logit = ops.linear(lat, w["w2"], bias=w["w0"])
         o = ops.empty((T, n))
         ops.linear_state(D[:, :n], D[:, n:2 * n], D[:, 2 * n:3 * n], o, st[:, off + W:off + self.state_floats], ctx, H=self.H,
-                         rep=1, dim=self.dim, vdim=self.dim, decay_logits=logit, bonus=w["u"])
+                         rep=1, dim=self.dim, vdim=self.dim, decay_logits=logit, bonus=w["u"], part_len=self.PART_LEN)
         ops.head_post(o, o, dv=self.dim, gate=D[:, 3 * n:], gate_silu=True, w=w["norm"], eps=ctx.eps, span=self.dim)
         return ops.linear(o, w["o"])
 

@@ -445,10 +445,12 @@ class LayerOps:
 
     def linear_state(self, q, k, v, out, state, ctx, *, H, rep, dim, vdim, act=False, unit_eps=0.0, q_scale=1.0,
                      decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False, dt_in=False, skip=None,
-                     decay_logits=None, bonus=None):
+                     decay_logits=None, bonus=None, part_len: int = 0):
         """dt_in: the state-space form, u = softplus(a + dt_bias) v; skip (H,): out += skip[h] v;
         decay_logits (T, H dim) with bonus (H, dim): a decay per key channel w = exp(-exp(decay_logits)) and
-        out = S^T q + (sum_i q_i bonus_i k_i) v with S the state before the token, then S <- diag(w) S + k v^T"""
+        out = S^T q + (sum_i q_i bonus_i k_i) v with S the state before the token, then S <- diag(w) S + k v^T;
+        part_len > 0 (with decay_logits, a prompt step): sequences longer than that are walked in parts of part_len
+        tokens at the same time (the state is linear in its start state, so the parts' contributions chain exactly)"""
         _, seqs, G = ctx.seq_tables()
         T, Hk = q.shape[0], H // rep
         # a prompt step does the per-token work (activation, unit lengths, k . q, decay, beta) in one parallel pass first
@@ -456,13 +458,21 @@ class LayerOps:
             prep = self.empty((T * (3 * H * dim + H),)) if T > SKINNY_ROWS else None
         else:
             prep = self.empty((T * (2 * Hk * dim + Hk + 2 * H),)) if T > SKINNY_ROWS else None
+        scratch, n_parts = None, 0
+        if decay_logits is not None and prep is not None and part_len > 0 and ctx.segments:
+            n_parts = max(-(-n // part_len) for _, n, _, _ in ctx.segments)
+            if n_parts > 1:
+                lanes = 1
+                while lanes * 8 < dim:
+                    lanes *= 2
+                scratch = self.empty((G * n_parts * (H * 8 * vdim * lanes + H * lanes * 8),))
         self._ok(self.lib.b200_lm_linear_state(
             q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(), out.stride(0),
             state.data_ptr(), state.stride(0), seqs.data_ptr(), G, ctx.slot.data_ptr(), ctx.pos.data_ptr(), H, rep, dim,
             vdim, int(act), float(unit_eps), float(q_scale), N.ptr(decay_const), N.ptr(a), a.stride(0) if a is not None else 0,
             N.ptr(A_log), N.ptr(dt_bias), N.ptr(b), b.stride(0) if b is not None else 0, int(delta), int(dt_in), N.ptr(skip),
             N.ptr(decay_logits), decay_logits.stride(0) if decay_logits is not None else 0, N.ptr(bonus),
-            N.ptr(prep), T, self.s),
+            N.ptr(prep), int(part_len) if scratch is not None else 0, n_parts, N.ptr(scratch), T, self.s),
             "lm_linear_state")
 
     def head_post(self, o, out, *, dv, gate=None, gate_per_head=False, gate_silu=False, w=None, eps=0.0, span=0,

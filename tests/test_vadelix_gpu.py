@@ -387,8 +387,11 @@ def test_projection_post_steps(case):
         assert (host(eng, keep) - vr).abs().max() < 2e-5
 
 
+@pytest.mark.parametrize("part_len", [0, 8, 5])
 @pytest.mark.parametrize("H,d", [(3, 8), (2, 12), (4, 32), (1, 64), (2, 100), (5, 4)])
-def test_state_with_a_decay_per_channel_in_portions_and_slots(H, d):
+def test_state_with_a_decay_per_channel_in_portions_and_slots(H, d, part_len):
+    """part_len: long portions are walked in parts of that many tokens at the same time (a portion of 17 tokens in 3 or 4
+    parts, one of 2 tokens beside one of 19 in one step, a last part of one token)"""
     eng = _eng()
     ops = eng.ops
     from mlx_vlm_b200.models.decoder_blocks import state_floats
@@ -418,11 +421,12 @@ def test_state_with_a_decay_per_channel_in_portions_and_slots(H, d):
     def run(ctx, parts):
         r, k, v, x = (dev(torch.cat(p)) for p in parts)
         o = dev(torch.zeros(r.shape[0], n))
-        ops.linear_state(r, k, v, o, st, ctx, H=H, rep=1, dim=d, vdim=d, decay_logits=x, bonus=dev(u, torch.bfloat16))
+        ops.linear_state(r, k, v, o, st, ctx, H=H, rep=1, dim=d, vdim=d, decay_logits=x, bonus=dev(u, torch.bfloat16),
+                         part_len=part_len)
         return host(eng, o)
 
     got, at = [], 0
-    for kk, cut in enumerate([17, 1, 1, 2, 20]):
+    for kk, cut in enumerate([17, 1, 1, 2, 20] if part_len != 5 else [21, 1, 1, 2, 16]):
         part = [[t[at:at + cut]] for t in a]
         if kk == 3:                   # b joins for one step, whole, in another slot
             y = run(_ctx(eng, pool, [(0, cut, 2, at), (cut, 19, 0, 0)]), [p + [t] for p, t in zip(part, b)])
