@@ -507,11 +507,12 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
                          const float* b, long ldb, int delta, int dt_in, const void* skip, const float* wraw, long ldwr,
                          const void* bonus, float* prep, int part_len, int n_parts, float* part_scratch, int T, void* stream);
 /* operands of the tensor-core attention of a prompt step: out[(t, r)] = bf16 of q[t][r * dim .. + dim) padded to Kp;
- * P[(t, r)][j] = softmax over the visible keys key0 + j (and sink[r]) of scale * S[(t, r)][j], bf16, zero elsewhere */
+ * P[(t, r)][j] = softmax over the visible keys key0 + j (and sink[r]) of scale * S[(t, r)][j], bf16, zero elsewhere;
+ * split: P rows are [hi | lo] (Sp columns each), lo the rounding error of hi (the operand of a two-part product) */
 int b200_lm_heads_to_bf16(const float* q, long ldq, int rep, int dim, void* out, int Kp, int T, void* stream);
 int b200_lm_sink_softmax_bf16(const float* S, long lds, const int* pos, int rep, const void* sink, float scale, int chunk,
-                              int window, int key0, float bias_exp, int head0, int H, int unit_sink, void* P, long ldp,
-                              int rows, int Sp, void* stream);
+                              int window, int key0, float bias_exp, int head0, int H, int unit_sink, int split, void* P,
+                              long ldp, int rows, int Sp, void* stream);
 /* out[t][c] = scale * o[t][c] * [rsqrt(mean over c's group of `span` + eps)] * [w[c mod w_len]] * [act(gate)];
  * gate_first: the gate is applied before the norm (the mean square is that of the gated numbers) */
 int b200_lm_head_post(const float* o, long ldi, const float* gate, long ldg, const void* w, int w_len, float eps, int span,

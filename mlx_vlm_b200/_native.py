@@ -146,7 +146,7 @@ LM_SIGNATURES = {
     "b200_lm_linear_state": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _F,
                                   _P, _P, _L, _P, _P, _P, _L, _I, _I, _P, _P, _L, _P, _P, _I, _I, _P, _I, _P]),
     "b200_lm_heads_to_bf16": (_I, [_P, _L, _I, _I, _P, _I, _I, _P]),
-    "b200_lm_sink_softmax_bf16": (_I, [_P, _L, _P, _I, _P, _F, _I, _I, _I, _F, _I, _I, _I, _P, _L, _I, _I, _P]),
+    "b200_lm_sink_softmax_bf16": (_I, [_P, _L, _P, _I, _P, _F, _I, _I, _I, _F, _I, _I, _I, _I, _P, _L, _I, _I, _P]),
     "b200_lm_head_post": (_I, [_P, _L, _P, _L, _P, _I, _F, _I, _I, _I, _I, _I, _F, _P, _L, _I, _I, _P]),
     "b200_lm_glu_clamp": (_I, [_P, _L, _P, _L, _F, _F, _F, _F, _P, _L, _I, _I, _P]),
     "b200_lm_glu_clamp_bf16": (_I, [_P, _L, _P, _L, _F, _F, _F, _F, _P, _I, _I, _P, _I, _P]),

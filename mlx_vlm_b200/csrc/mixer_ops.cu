@@ -380,9 +380,9 @@ __global__ void sink_attention_merge_kernel(const float* __restrict__ part, int 
   __syncthreads();
   const float inv = inv_s;
   for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
-    float a = 0.f;
-    for (int s = 0; s < n_split; ++s)
-      if (wgt[s] != 0.f) a = fmaf(pp[(long)s * row + d], wgt[s], a);
+    float a = 0.f;                 // a split without keys left zeros and weighs zero: its term adds nothing, and the
+#pragma unroll 8                   // loads of all splits are in flight together
+    for (int s = 0; s < n_split; ++s) a = fmaf(pp[(long)s * row + d], wgt[s], a);
     out[(long)t * ldo + (long)h * vdim + d] = a * inv;
   }
 }
@@ -695,6 +695,153 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(StateP p) {
     for (int i = 0; i < LS_R; ++i) st[(((long)h * LS_R + i) * p.vdim + col) * P + r] = S[i];
   }
 }
+// The walk with a decay per key channel over PREPARED inputs (a prompt step), two value columns per thread: the staged
+// k, q, w rows of a token are loaded from shared memory once for both columns, which is what bounds the walk (every
+// thread reads 24 floats per token for 16 multiply-adds per column).  Same parts scheme and state layout as above.
+template <int P, int NC, bool LOCAL>
+__global__ void __launch_bounds__(LS_THREADS) channel_state_kernel(StateP p) {
+  constexpr int CB = LS_THREADS / P, CBN = CB * NC, LD = P * LS_RS, DKP = P * LS_R;
+  constexpr int CT = P >= 32 ? LS_CT / 2 : LS_CT;
+  constexpr int NQK = (CT * DKP + LS_THREADS - 1) / LS_THREADS, NV = (CT * CBN + LS_THREADS - 1) / LS_THREADS;
+  __shared__ __align__(16) float ks[CT][LD], ws[CT][LD], qs[LOCAL ? 1 : CT][LOCAL ? 4 : LD];
+  __shared__ float vs[CT][CBN];
+  __shared__ float kq[CT];
+  const int seq = p.n_parts > 0 ? blockIdx.x / p.n_parts : blockIdx.x, part = p.n_parts > 0 ? blockIdx.x % p.n_parts : 0;
+  int start = p.seqs[2 * seq], rows = p.seqs[2 * seq + 1];
+  bool last_part = true;
+  if (p.n_parts > 0) {
+    const int n = (rows + p.part_len - 1) / p.part_len;
+    if (part >= (LOCAL ? n - 1 : n)) return;
+    last_part = part == n - 1;
+    start += part * p.part_len;
+    rows = min(p.part_len, rows - part * p.part_len);
+  }
+  const int h = blockIdx.y;
+  const int cj = threadIdx.x / P, r = threadIdx.x % P, col0 = blockIdx.z * CBN + cj * NC;
+  float S[NC][LS_R], Dacc[LOCAL ? LS_R : 1];
+  if (LOCAL) {
+#pragma unroll
+    for (int i = 0; i < LS_R; ++i) Dacc[i] = 1.f;
+  }
+  const long head_floats = (long)LS_R * p.vdim * P;
+  const float* st0 = p.state + (long)p.slot[start] * p.slot_stride;
+  if (!LOCAL && part > 0) st0 = p.part_state + ((long)seq * p.n_parts + part - 1) * p.H * head_floats;
+  const bool from_state = !LOCAL && (part > 0 || p.pos[start] > 0);
+#pragma unroll
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int i = 0; i < LS_R; ++i)
+      S[c][i] = (from_state && col0 + c < p.vdim) ? st0[(((long)h * LS_R + i) * p.vdim + col0 + c) * P + r] : 0.f;
+  float rk[NQK], rw[NQK], rq[LOCAL ? 1 : NQK], rv[NV], rkq = 0.f;
+  auto request = [&](int c0) {
+    const int nc = min(CT, rows - c0);
+#pragma unroll
+    for (int n = 0; n < NQK; ++n) {
+      const int e = threadIdx.x + n * LS_THREADS, tk = e / DKP, i = e % DKP;
+      const bool ok = tk < nc && i < p.dim;
+      const long t = start + c0 + tk;
+      rk[n] = ok ? p.k[t * p.ldk + (long)h * p.dim + i] : 0.f;
+      rw[n] = ok ? p.wdec[t * p.ldw + (long)h * p.dim + i] : 0.f;
+      if (!LOCAL) rq[n] = ok ? p.q[t * p.ldq + (long)h * p.dim + i] : 0.f;
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int e = threadIdx.x + n * LS_THREADS, tk = e / CBN, cc = blockIdx.z * CBN + e % CBN;
+      rv[n] = (tk < nc && cc < p.vdim) ? p.v[(long)(start + c0 + tk) * p.ldv + (long)h * p.vdim + cc] : 0.f;
+    }
+    if (!LOCAL && (int)threadIdx.x < nc) rkq = p.kq_in[(long)(start + c0 + threadIdx.x) * p.H + h];
+  };
+  request(0);
+  for (int c0 = 0; c0 < rows; c0 += CT) {
+    const int nc = min(CT, rows - c0);
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < NQK; ++n) {
+      const int e = threadIdx.x + n * LS_THREADS, tk = e / DKP, i = e % DKP;
+      if (e < CT * DKP) {
+        const int at = (i / LS_R) * LS_RS + (i % LS_R);
+        ks[tk][at] = rk[n]; ws[tk][at] = rw[n];
+        if (!LOCAL) qs[tk][at] = rq[n];
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int e = threadIdx.x + n * LS_THREADS;
+      if (e < CT * CBN) vs[e / CBN][e % CBN] = rv[n];
+    }
+    if (!LOCAL && (int)threadIdx.x < nc) kq[threadIdx.x] = rkq;
+    __syncthreads();
+    if (c0 + CT < rows) request(c0 + CT);
+    float* op = p.out + (long)(start + c0) * p.ldo + (long)h * p.vdim + col0;
+    const float* kp = &ks[0][r * LS_RS];
+    const float* wp = &ws[0][r * LS_RS];
+    const float* qp = &qs[0][LOCAL ? 0 : r * LS_RS];
+#pragma unroll 2
+    for (int tk = 0; tk < nc; ++tk, op += p.ldo, kp += LD, wp += LD) {
+      const float4 k0 = *reinterpret_cast<const float4*>(kp), k1 = *reinterpret_cast<const float4*>(kp + 4);
+      const float4 w0 = *reinterpret_cast<const float4*>(wp), w1 = *reinterpret_cast<const float4*>(wp + 4);
+      const float k_[LS_R] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+      const float w_[LS_R] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      float vin[NC];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) vin[c] = vs[tk][cj * NC + c];
+      if (LOCAL) {
+#pragma unroll
+        for (int i = 0; i < LS_R; ++i) Dacc[i] *= w_[i];
+      } else {
+        const float4 q0 = *reinterpret_cast<const float4*>(qp), q1 = *reinterpret_cast<const float4*>(qp + 4);
+        qp += LD;
+        const float q_[LS_R] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        float dq[NC];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          float b0 = 0.f, b1 = 0.f;
+#pragma unroll
+          for (int i = 0; i < LS_R; i += 2) { b0 = fmaf(S[c][i], q_[i], b0); b1 = fmaf(S[c][i + 1], q_[i + 1], b1); }
+          dq[c] = b0 + b1;
+        }
+#pragma unroll
+        for (int o = 1; o < P; o <<= 1)
+#pragma unroll
+          for (int c = 0; c < NC; ++c) dq[c] += __shfl_xor_sync(0xffffffffu, dq[c], o);
+        if (r == 0) {
+#pragma unroll
+          for (int c = 0; c < NC; ++c)
+            if (col0 + c < p.vdim) op[c] = fmaf(vin[c], kq[tk], dq[c]);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < LS_R; ++i) S[c][i] = fmaf(k_[i], vin[c], w_[i] * S[c][i]);
+    }
+  }
+  if (LOCAL) {
+    float* sl = p.part_state + ((long)seq * p.n_parts + part) * p.H * head_floats;
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+      if (col0 + c < p.vdim) {
+#pragma unroll
+        for (int i = 0; i < LS_R; ++i) sl[(((long)h * LS_R + i) * p.vdim + col0 + c) * P + r] = S[c][i];
+      }
+    if (col0 == 0) {
+      float* dl = p.part_decay + (((long)seq * p.n_parts + part) * p.H + h) * (P * LS_R);
+#pragma unroll
+      for (int i = 0; i < LS_R; ++i) dl[r * LS_R + i] = Dacc[i];
+    }
+    return;
+  }
+  if (last_part) {
+    float* st = p.state + (long)p.slot[start] * p.slot_stride;
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+      if (col0 + c < p.vdim) {
+#pragma unroll
+        for (int i = 0; i < LS_R; ++i) st[(((long)h * LS_R + i) * p.vdim + col0 + c) * P + r] = S[c][i];
+      }
+  }
+}
+
 // the start state of every part after a sequence's first: S <- diag(part's decay product) S + S_local, part after part
 __global__ void state_parts_chain_kernel(StateP p, int P) {
   const int seq = blockIdx.x, h = blockIdx.y;
@@ -866,8 +1013,8 @@ __global__ void heads_to_bf16_kernel(const float* __restrict__ q, long ldq, int 
 }
 __global__ void sink_softmax_bf16_kernel(const float* __restrict__ S, long lds, const int* __restrict__ pos, int rep,
                                          const bf16* __restrict__ sink, float scale, int chunk, int window, int key0,
-                                         float bias_exp, int head0, int H, int unit_sink, bf16* __restrict__ P, long ldp,
-                                         int Sp) {
+                                         float bias_exp, int head0, int H, int unit_sink, int split,
+                                         bf16* __restrict__ P, long ldp, int Sp) {
   __shared__ float red[32];
   const long r = blockIdx.x;
   const int ps = pos[r / rep];
@@ -891,8 +1038,14 @@ __global__ void sink_softmax_bf16_kernel(const float* __restrict__ S, long lds, 
   for (int j = j0 + threadIdx.x; j <= j1; j += blockDim.x) sum += expf(sc(j) - m);
   const float tot = block_sum_fixed(sum, red) + ((sink || unit_sink) ? expf(sk - m) : 0.f);
   const float inv = 1.0f / tot;
-  for (int j = threadIdx.x; j < Sp; j += blockDim.x)
-    P[r * ldp + j] = f2bf((j >= j0 && j <= j1) ? expf(sc(j) - m) * inv : 0.f);
+  // split: the probability as two bf16 parts [hi | lo] (Sp columns each), lo = the rounding error of hi: the next
+  // product multiplies both by the values and sums them in its fp32 accumulator, so the weights keep 16 mantissa bits
+  for (int j = threadIdx.x; j < Sp; j += blockDim.x) {
+    const float pr = (j >= j0 && j <= j1) ? expf(sc(j) - m) * inv : 0.f;
+    const bf16 hi = f2bf(pr);
+    P[r * ldp + j] = hi;
+    if (split) P[r * ldp + Sp + j] = f2bf(pr - bf2f(hi));
+  }
 }
 
 unsigned long long g_sink_attr_f32 = 0, g_sink_attr_bf16 = 0;
@@ -1029,10 +1182,12 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
     if (parts) {     /* scratch: n_seq * n_parts * (H LS_R vdim PP + H PP LS_R) floats */                        \
       p.part_len = part_len; p.n_parts = n_parts; p.part_state = part_scratch;                                   \
       p.part_decay = part_scratch + (long)n_seq * n_parts * H * LS_R * vdim * PP;                                \
-      const dim3 pgrid(n_seq * n_parts, H, grid.z);                                                              \
-      linear_state_kernel<PP, false, true, true><<<pgrid, block, 0, cs>>>(p);                                    \
+      const dim3 pgrid(n_seq * n_parts, H, cdiv(vdim, 2 * (LS_THREADS / PP)));                                   \
+      channel_state_kernel<PP, 2, true><<<pgrid, block, 0, cs>>>(p);                                             \
       state_parts_chain_kernel<<<dim3(n_seq, H, cdiv(LS_R * vdim * PP, 1024)), 256, 0, cs>>>(p, PP);             \
-      linear_state_kernel<PP, false, true, false><<<pgrid, block, 0, cs>>>(p);                                   \
+      channel_state_kernel<PP, 2, false><<<pgrid, block, 0, cs>>>(p);                                            \
+    } else if (chan && prep) {                                                                                   \
+      channel_state_kernel<PP, 2, false><<<dim3(n_seq, H, cdiv(vdim, 2 * (LS_THREADS / PP))), block, 0, cs>>>(p); \
     } else if (chan) linear_state_kernel<PP, false, true><<<grid, block, 0, cs>>>(p);                            \
     else if (delta) linear_state_kernel<PP, true, false><<<grid, block, 0, cs>>>(p);                             \
     else linear_state_kernel<PP, false, false><<<grid, block, 0, cs>>>(p);                                       \
@@ -1056,11 +1211,11 @@ int b200_lm_heads_to_bf16(const float* q, long ldq, int rep, int dim, void* out,
 }
 
 int b200_lm_sink_softmax_bf16(const float* S, long lds, const int* pos, int rep, const void* sink, float scale, int chunk,
-                              int window, int key0, float bias_exp, int head0, int H, int unit_sink, void* P, long ldp,
-                              int rows, int Sp, void* st) {
+                              int window, int key0, float bias_exp, int head0, int H, int unit_sink, int split, void* P,
+                              long ldp, int rows, int Sp, void* st) {
   B200_REQUIRE(S && pos && P && rows > 0 && rep > 0 && Sp > 0 && key0 >= 0, "lm_sink_softmax_bf16: bad argument");
   sink_softmax_bf16_kernel<<<rows, 256, 0, (cudaStream_t)st>>>(S, lds, pos, rep, (const bf16*)sink, scale, chunk, window,
-                                                                key0, bias_exp, head0, H > 0 ? H : 1, unit_sink, (bf16*)P, ldp, Sp);
+                                                                key0, bias_exp, head0, H > 0 ? H : 1, unit_sink, split, (bf16*)P, ldp, Sp);
   B200_CHECK_LAUNCH();
   return B200_OK;
 }

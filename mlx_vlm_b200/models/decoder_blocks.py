@@ -1146,8 +1146,9 @@ class GroupedAttention:
     def _attend_prompt(self, ctx: StepCtx, q, all_rows, slot_index: int, pos, o, p0: int, n: int):
         """A portion of a prompt (positions p0 .. p0 + n - 1 of one slot) as two tcgen05 products per key/value head:
         the head's cached key columns are the weight-major operand of the scores of the query heads that share it, an
-        fp32 softmax over the visible keys (distance bias and sink included) writes bf16 probabilities, and the head's
-        value columns, transposed, are the operand of the weighted sum.  Queries are taken in chunks that bound the
+        fp32 softmax over the visible keys (distance bias and sink included) writes every probability as two bf16 parts
+        (the second the rounding error of the first, so the weights keep 16 mantissa bits), and the head's value
+        columns, transposed, are the operand of the weighted sum over both parts.  Queries are taken in chunks that bound the
         score buffer; with a window a chunk is about a window long and meets only the keys from its first query's
         first visible key on."""
         ops, H, G, d, dv = ctx.ops, self.H, self.G, self.dim, self.vdim
@@ -1171,12 +1172,12 @@ class GroupedAttention:
                     qb16 = ops.heads_to_bf16(q[b:b + mm, g * rep * d:], rep, d)
                     sc = ops.empty((mm * rep, S))
                     ops.tc_gemm(qb16, keys, sc, N_=S, K=d, ldw=rows.stride(0))
-                    P = ops.empty((mm * rep, Sp), torch.bfloat16)
+                    P = ops.empty((mm * rep, 2 * Sp), torch.bfloat16)
                     ops.sink_softmax_bf16(sc, pos[b:b + mm], rep, None if sink is None else sink[g * rep:], self.scale, 0,
                                           self.window, key0, P, bias_exp=self.bias_exp, head0=g * rep, H=H,
-                                          unit_sink=self.sink == "unit")
+                                          unit_sink=self.sink == "unit", split=True)
                     og = ops.empty((mm * rep, dv))
-                    ops.tc_gemm(P, vt, og, N_=dv, K=Sp)
+                    ops.tc_gemm(P, vt, og, N_=dv, K=Sp, parts=2)
                     ops.head_post(og.view(mm, rep * dv), o[b:b + mm, g * rep * dv:(g + 1) * rep * dv], dv=dv)
 
 

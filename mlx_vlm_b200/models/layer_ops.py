@@ -436,12 +436,14 @@ class LayerOps:
         return out
 
     def sink_softmax_bf16(self, S, pos, rep, sink, scale, chunk, window, key0, P, bias_exp: float = 0.0, head0: int = 0,
-                          H: int = 1, unit_sink: bool = False):
-        """head0, H: the first head of the rows' group and the number of heads (they fix the slopes of the distance bias)"""
+                          H: int = 1, unit_sink: bool = False, split: bool = False):
+        """head0, H: the first head of the rows' group and the number of heads (they fix the slopes of the distance bias);
+        split: P (rows, 2 Sp) gets every probability as two bf16 parts [hi | lo], the operand of `tc_gemm(parts=2)`"""
         self._ok(self.lib.b200_lm_sink_softmax_bf16(S.data_ptr(), S.stride(0), pos.data_ptr(), rep, N.ptr(sink), float(scale),
                                                     int(chunk), int(window), int(key0), float(bias_exp), int(head0), int(H),
-                                                    int(unit_sink), P.data_ptr(), P.stride(0),
-                                                    S.shape[0], P.shape[1], self.s), "lm_sink_softmax_bf16")
+                                                    int(unit_sink), int(split), P.data_ptr(), P.stride(0),
+                                                    S.shape[0], P.shape[1] // 2 if split else P.shape[1], self.s),
+                 "lm_sink_softmax_bf16")
 
     def linear_state(self, q, k, v, out, state, ctx, *, H, rep, dim, vdim, act=False, unit_eps=0.0, q_scale=1.0,
                      decay_const=None, a=None, A_log=None, dt_bias=None, b=None, delta=False, dt_in=False, skip=None,
