@@ -466,10 +466,11 @@ int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long l
                        int act, const void* bias, int residual, int T, void* stream);
 /* token shift: M[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s] (mu: bf16 [n_mix][C]); the row before a sequence's first token
  * of the step is state[slot] ([C]; zeros at position 0), which then keeps the sequence's last row.  single: every
- * sequence of the step brings one token (the update happens in the same launch) */
-int b200_lm_token_shift(const float* h, long ldh, const void* mu, float* M, long ldm, long mix_stride, float* state,
+ * sequence of the step brings one token (the update happens in the same launch); out_bf16: M is bf16 rows of ldm >= C
+ * columns, zero beyond C (operands of the tensor-core products), strides in elements */
+int b200_lm_token_shift(const float* h, long ldh, const void* mu, void* M, long ldm, long mix_stride, float* state,
                         long slot_stride, const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C,
-                        int n_mix, int single, int T, void* stream);
+                        int n_mix, int single, int out_bf16, int T, void* stream);
 /* rotate-half rotary (first rot_dims of every head) on Q in place and on K; cache[slot[t]][pos[t]] = [K | V].
  * Optional steps before that: qn_w / kn_w (bf16 [H dim] / [G dim]): RMS norm (eps) over the whole query / key projection
  * times the weight; qt_every > 0: Q times 1 + qt_coef ln(floor((pos + 1) / qt_every) + 1); v_unit: every value head

@@ -93,7 +93,8 @@ struct ShiftP {
   float* state; long slot_stride;  // per slot [C]
   const int *slot, *pos, *first;
   int C, n_mix, single;            // single: every sequence of the step is one token
-};
+  bf16* Mb; long ldb, mixb_stride; // != NULL: the mixes are written as bf16 operand rows of ldb >= C columns (zero padding
+};                                 // beyond C) for the tensor-core products that read them, instead of fp32 rows
 __global__ void token_shift_kernel(ShiftP p) {
   const int t = blockIdx.x;
   const bool head = p.first[t] == t;
@@ -103,10 +104,16 @@ __global__ void token_shift_kernel(ShiftP p) {
     const float x = p.h[(long)t * p.ldh + c];
     const float prev = head ? (fresh ? 0.f : st[c]) : p.h[(long)(t - 1) * p.ldh + c];
     const float d = prev - x;
-    for (int s = 0; s < p.n_mix; ++s)
-      p.M[(long)s * p.mix_stride + (long)t * p.ldm + c] = fmaf(d, bf2f(p.mu[(long)s * p.C + c]), x);
+    for (int s = 0; s < p.n_mix; ++s) {
+      const float m = fmaf(d, bf2f(p.mu[(long)s * p.C + c]), x);
+      if (p.Mb) p.Mb[(long)s * p.mixb_stride + (long)t * p.ldb + c] = f2bf(m);
+      else p.M[(long)s * p.mix_stride + (long)t * p.ldm + c] = m;
+    }
     if (p.single) st[c] = x;
   }
+  if (p.Mb)
+    for (int c = p.C + blockIdx.y * blockDim.x + threadIdx.x; c < p.ldb; c += blockDim.x * gridDim.y)
+      for (int s = 0; s < p.n_mix; ++s) p.Mb[(long)s * p.mixb_stride + (long)t * p.ldb + c] = f2bf(0.f);
 }
 __global__ void token_shift_state_kernel(ShiftP p, const int* __restrict__ seqs) {
   const int start = seqs[2 * blockIdx.x], rows = seqs[2 * blockIdx.x + 1];
@@ -1073,12 +1080,14 @@ int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long l
   return B200_OK;
 }
 
-int b200_lm_token_shift(const float* h, long ldh, const void* mu, float* M, long ldm, long mix_stride, float* state,
+int b200_lm_token_shift(const float* h, long ldh, const void* mu, void* M, long ldm, long mix_stride, float* state,
                         long slot_stride, const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C,
-                        int n_mix, int single, int T, void* st) {
+                        int n_mix, int single, int out_bf16, int T, void* st) {
   B200_REQUIRE(h && mu && M && state && slot && pos && first && seqs && T > 0 && n_seq > 0 && C > 0 && n_mix > 0,
                "lm_token_shift: bad argument");
-  ShiftP p{h, ldh, (const bf16*)mu, M, ldm, mix_stride, state, slot_stride, slot, pos, first, C, n_mix, single};
+  B200_REQUIRE(!out_bf16 || ldm >= C, "lm_token_shift: operand rows of %ld columns for %d channels", ldm, C);
+  ShiftP p{h, ldh, (const bf16*)mu, out_bf16 ? nullptr : (float*)M, ldm, mix_stride, state, slot_stride, slot, pos, first, C, n_mix, single,
+           out_bf16 ? (bf16*)M : nullptr, ldm, mix_stride};
   const int by = cdiv(C, 256) < 8 ? cdiv(C, 256) : 8;
   token_shift_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();

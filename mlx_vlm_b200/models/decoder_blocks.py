@@ -1236,23 +1236,28 @@ class TokenShiftState:
     def forward(self, ctx: StepCtx, h: torch.Tensor) -> torch.Tensor:
         ops, w, T, n, W = ctx.ops, self.w, h.shape[0], self.n, self.W
         st, off = ctx.pool.state, self.state_off
-        M = ops.token_shift(h, w["mu"], st[:, off:off + W], ctx)          # (5, T, W)
         D = ops.empty((T, 4 * n))                                          # r | k | v | gate
-        if ops.tc_ok(T, W):           # a prompt: four tensor-core products
-            for i in range(4):
-                ops.linear(M[i], w["rkvg"][i], out=D[:, i * n:(i + 1) * n])
-        else:                         # few rows: ONE launch over the four (input, weight) pairs
-            ops.gemm(M, w["rkvg"], D, M=T, N_=n, K=W, ldx=W, xb=T * W, wb=n * W, ldy=4 * n, yb=n, batch=4)
-        logit = None
-        if ops.tc_ok(T, W, self.rank):    # a prompt: the tanh is applied while the latent rows are rounded to the operand
+        logit = M = None
+        if ops.tc_ok(T, W, self.rank) and n % 4 == 0 and w["rkvg"].data_ptr() % 16 == 0:
+            # a prompt: the mixes are written as the bf16 operands of five tensor-core products; the tanh of the decay
+            # projection is applied while its latent rows are rounded to the next operand
             try:
+                Mb = ops.token_shift(h, w["mu"], st[:, off:off + W], ctx, operands=True)      # (5, T, ceil64(W)) bf16
+                for i in range(4):
+                    ops.tc_gemm(Mb[i], w["rkvg"][i], D[:, i * n:(i + 1) * n], N_=n, K=W)
+                lat = ops.empty((T, self.rank))
+                ops.tc_gemm(Mb[4], w["w1"], lat, N_=self.rank, K=W)
                 logit = ops.empty((T, n))
-                ops.tc_gemm(ops.to_bf16(ops.linear(M[4], w["w1"]), self.rank, act=ACT_TANH), w["w2"], logit, N_=n, K=self.rank,
-                            bias=w["w0"])
-            except _B200Error as e:
-                ops.tc_refused(e)
+                ops.tc_gemm(ops.to_bf16(lat, self.rank, act=ACT_TANH), w["w2"], logit, N_=n, K=self.rank, bias=w["w0"])
+            except _B200Error as e:       # the slot's previous input is already replaced: the shift is not run again,
+                ops.tc_refused(e)         # the row kernels read the rounded mixes
                 logit = None
-        if logit is None:
+                with torch.cuda.stream(ops.stream):
+                    M = Mb[..., :W].float()
+        if logit is None:             # few rows: ONE launch over the four (input, weight) pairs
+            if M is None:
+                M = ops.token_shift(h, w["mu"], st[:, off:off + W], ctx)      # (5, T, W)
+            ops.gemm(M, w["rkvg"], D, M=T, N_=n, K=W, ldx=W, xb=T * W, wb=n * W, ldy=4 * n, yb=n, batch=4)
             lat = ops.linear(M[4], w["w1"], epi=EPI_SOFTCAP, epi_param=1.0)    # tanh
             logit = ops.linear(lat, w["w2"], bias=w["w0"])
         o = ops.empty((T, n))

@@ -380,16 +380,17 @@ class LayerOps:
                  "lm_short_conv")
         return Y
 
-    def token_shift(self, h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, ctx) -> torch.Tensor:
+    def token_shift(self, h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, ctx, operands: bool = False) -> torch.Tensor:
         """-> M (n_mix, T, C): M[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s]; state (slots, C) fp32 view of the pool: the
-        last input of every slot's sequence (read by the first token of a step, then replaced)"""
+        last input of every slot's sequence (read by the first token of a step, then replaced).  operands: M is
+        (n_mix, T, ceil64(C)) bf16, zero-padded: the rows `tc_gemm` reads"""
         T, C = h.shape
         first, seqs, G = ctx.seq_tables()
-        M = self.empty((mu.shape[0], T, C))
+        M = self.empty((mu.shape[0], T, (C + 63) // 64 * 64), torch.bfloat16) if operands else self.empty((mu.shape[0], T, C))
         self._ok(self.lib.b200_lm_token_shift(h.data_ptr(), h.stride(0), mu.data_ptr(), M.data_ptr(), M.stride(1), M.stride(0),
                                               state.data_ptr(), state.stride(0), ctx.slot.data_ptr(), ctx.pos.data_ptr(),
                                               first.data_ptr(), seqs.data_ptr(), G, C, mu.shape[0],
-                                              int(ctx.segments is None), T, self.s), "lm_token_shift")
+                                              int(ctx.segments is None), int(operands), T, self.s), "lm_token_shift")
         return M
 
     def qkv_post(self, Q, K, V, cache_layer, slot, pos, cs, H, G, dim, vdim, rot_dims, *, q_norm=None, k_norm=None,
