@@ -483,7 +483,7 @@ __global__ void state_prep_kernel(StatePrepP p) {
       float a = kr[i], b = qr[i];
       if (p.act) { a = silu_exact(a); b = silu_exact(b); }
       a *= ik; b *= iq;
-      ko[i] = a; qo[i] = b;
+      if (!p.wraw) { ko[i] = a; qo[i] = b; }        // (a decay per channel leaves q, k as they are: the walk reads the originals)
       dot = p.wraw ? fmaf(a * b, bf2f(p.bonus[(long)hk * p.dim + i]), dot) : fmaf(a, b, dot);
     }
     dot = warp_sum(dot);
@@ -1181,7 +1181,8 @@ int b200_lm_linear_state(const float* q, long ldq, const float* k, long ldk, con
     if (chan) { p.wdec = dec; p.ldw = n; }
     state_prep_kernel<<<T, 128, 0, cs>>>(pp);
     B200_CHECK_LAUNCH();
-    p.q = qn; p.ldq = n; p.k = kn; p.ldk = n; p.kq_in = kq; p.dec_in = dec; p.bet_in = bet;
+    if (!chan) { p.q = qn; p.ldq = n; p.k = kn; p.ldk = n; }
+    p.kq_in = kq; p.dec_in = dec; p.bet_in = bet;
   }
   const dim3 block(LS_THREADS);
   const bool parts = chan && prep && n_parts > 1 && part_len > 0 && part_scratch;
