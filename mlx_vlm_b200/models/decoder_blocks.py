@@ -1237,7 +1237,7 @@ class TokenShiftState:
         ops, w, T, n, W = ctx.ops, self.w, h.shape[0], self.n, self.W
         st, off = ctx.pool.state, self.state_off
         D = ops.empty((T, 4 * n))                                          # r | k | v | gate
-        logit = M = None
+        logit = M = Mb = None
         if ops.tc_ok(T, W, self.rank) and n % 4 == 0 and w["rkvg"].data_ptr() % 16 == 0:
             # a prompt: the mixes are written as the bf16 operands of five tensor-core products; the tanh of the decay
             # projection is applied while its latent rows are rounded to the next operand
@@ -1252,6 +1252,8 @@ class TokenShiftState:
             except _B200Error as e:       # the slot's previous input is already replaced: the shift is not run again,
                 ops.tc_refused(e)         # the row kernels read the rounded mixes
                 logit = None
+                if Mb is None:
+                    raise
                 with torch.cuda.stream(ops.stream):
                     M = Mb[..., :W].float()
         if logit is None:             # few rows: ONE launch over the four (input, weight) pairs
