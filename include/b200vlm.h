@@ -460,10 +460,11 @@ int b200_lm_advance_rows(const int* sampled, int* tok, int* pos, const int* acti
 /* sequence, seqs[g] = (first row, rows).  State buffers are fp32 per slot.    */
 /* ------------------------------------------------------------------------- */
 /* Y[t][c] = act(bias[c] + [U[t][c] if residual] + sum_j w[c][j] U[t - (taps-1) + j][c]) (bias may be NULL); inputs before the step come from state[slot] = the
- * taps-1 inputs before the step's first token ([taps-1][C]), zeros before position 0; the state is then advanced */
+ * taps-1 inputs before the step's first token ([taps-1][C]), zeros before position 0; the state is then advanced (single:
+ * every sequence of the step is one token, and the same launch advances it) */
 int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
                        const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
-                       int act, const void* bias, int residual, int T, void* stream);
+                       int act, const void* bias, int residual, int single, int T, void* stream);
 /* token shift: M[s][t] = h[t] + (h[t - 1] - h[t]) * mu[s] (mu: bf16 [n_mix][C]); the row before a sequence's first token
  * of the step is state[slot] ([C]; zeros at position 0), which then keeps the sequence's last row.  single: every
  * sequence of the step brings one token (the update happens in the same launch); out_bf16: M is bf16 rows of ldm >= C

@@ -137,7 +137,7 @@ LM_SIGNATURES = {
     "b200_f32_split": (_I, [_P, _L, _P, _L, _I, _I, _I, _P]),
     "b200_lm_advance_rows": (_I, [_P, _P, _P, _P, _P, _I, _I, _P, _P, _P, _I, _P]),
     # csrc/mixer_ops.cu
-    "b200_lm_short_conv": (_I, [_P, _L, _P, _P, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _P]),
+    "b200_lm_short_conv": (_I, [_P, _L, _P, _P, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _I, _P]),
     "b200_lm_token_shift": (_I, [_P, _L, _P, _P, _L, _L, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "b200_lm_qkv_post": (_I, [_P, _L, _P, _L, _P, _L, _P, _I, _L, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _F, _I, _F, _I, _P,
                               _P, _L, _P, _L, _I, _P]),

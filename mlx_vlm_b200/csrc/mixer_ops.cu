@@ -48,7 +48,8 @@ struct ConvP {
   int C, taps, act;
   const bf16* bias;                // [C] or NULL
   int residual;                    // the input itself is added to the convolution's output (before the activation)
-};
+  int single;                      // every sequence of the step is one token: the thread that read a channel's kept inputs
+};                                 // also advances them (no second launch)
 __global__ void short_conv_kernel(ConvP p) {
   const int t = blockIdx.x;
   const int back = t - p.first[t], ps = p.pos[t];
@@ -64,6 +65,16 @@ __global__ void short_conv_kernel(ConvP p) {
       a = fmaf(bf2f(p.w[(long)c * p.taps + j]), u, a);
     }
     p.Y[(long)t * p.ldy + c] = p.act ? silu_exact(a) : a;
+    if (p.single) {                // entry j takes entry j + 1 (zero while that lies before the sequence), the last one the input
+      float* sw = p.state + (long)p.slot[t] * p.slot_stride;
+      const int n = p.taps - 1;
+      for (int j = 0; j < n; ++j) {
+        float v = 0.f;
+        if (j == n - 1) v = p.U[(long)t * p.ldu + c];
+        else if (ps + 1 - n + j >= 0) v = sw[(long)(j + 1) * p.C + c];
+        sw[(long)j * p.C + c] = v;
+      }
+    }
   }
 }
 // after the step: the slot keeps the last taps - 1 inputs of its sequence.  A thread owns a channel; entry j takes
@@ -1066,14 +1077,14 @@ extern "C" {
 
 int b200_lm_short_conv(const float* U, long ldu, const void* w, float* Y, long ldy, float* state, long slot_stride,
                        const int* slot, const int* pos, const int* first, const int* seqs, int n_seq, int C, int taps,
-                       int act, const void* bias, int residual, int T, void* st) {
+                       int act, const void* bias, int residual, int single, int T, void* st) {
   B200_REQUIRE(U && w && Y && (state || taps == 1) && slot && pos && first && seqs && T > 0 && n_seq > 0 && C > 0 && taps > 0,
                "lm_short_conv: bad argument");     // one tap keeps nothing between steps
-  ConvP p{U, ldu, (const bf16*)w, Y, ldy, state, slot_stride, slot, pos, first, C, taps, act, (const bf16*)bias, residual};
+  ConvP p{U, ldu, (const bf16*)w, Y, ldy, state, slot_stride, slot, pos, first, C, taps, act, (const bf16*)bias, residual, single};
   const int by = cdiv(C, 256) < 8 ? cdiv(C, 256) : 8;
   short_conv_kernel<<<dim3(T, by), 256, 0, (cudaStream_t)st>>>(p);
   B200_CHECK_LAUNCH();
-  if (taps > 1) {
+  if (taps > 1 && !single) {
     conv_state_kernel<<<dim3(n_seq, by), 256, 0, (cudaStream_t)st>>>(p, seqs);
     B200_CHECK_LAUNCH();
   }

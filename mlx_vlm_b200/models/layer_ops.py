@@ -376,7 +376,7 @@ class LayerOps:
                                              state.data_ptr() if state.numel() else 0, state.stride(0), ctx.slot.data_ptr(),
                                              ctx.pos.data_ptr(),
                                              first.data_ptr(), seqs.data_ptr(), G, C, w.shape[1], int(act), N.ptr(bias),
-                                             int(residual), T, self.s),
+                                             int(residual), int(ctx.segments is None), T, self.s),
                  "lm_short_conv")
         return Y
 
